@@ -1,0 +1,281 @@
+"""The B200 sparse-attention backend: a drop-in for the reference's
+``HybridSparseBackend`` (attention/sparse/backend.py:27-255) behind the same
+duck-typed protocol the forward boundary calls
+(attention_forward.py:99-128,148-246):
+
+    prepare(q, k, v, *, layer_index, transformer_options) -> prepared
+    prepare_projected(projected, *, layer_index, transformer_options) -> prepared
+    execute(prepared) -> HND tensor (1,H,S,128) in the input dtype
+
+``prepare`` runs, on torch's current stream and without a host sync:
+column statistics (K mean, V amax) -> INT8 Q/K blocks with FP64 tile means ->
+FP8 V carrier -> router.  ``execute`` launches the tcgen05 attention kernel.
+There is no fallback of any kind: a device that is not sm_100, a missing
+native library or a failed launch raises ``SparseSageError``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native, ops
+from .carriers import PreparedFusedQKV, PreparedHybrid, PreparedSparse, validate_prepared_fused_qkv
+from .config import MODE_SAGE128_FUSED_QKV, HybridSparseConfig, resolve_video_budget
+from .errors import FusedQKVError, SparseRouterError, SparseSageError
+from .router import KV_TILE, Q_TILE, SparseTileRouter
+from .runtime import get_runtime_snapshot
+
+V_QUANT_BOUND = 448.0  # FP32 accumulation (reference: sparse_sage.py:296)
+
+
+def preflight():
+    """Raise ``SparseSageError`` unless the native library loads and the
+    current device is sm_100 (reference: sparse_sage.py:261-310)."""
+    if not torch.cuda.is_available():
+        raise SparseSageError("Hybrid Sparse Attention requires CUDA")
+    try:
+        capability = ops.device_capability()
+    except _native.NativeError as exc:
+        raise SparseSageError("B200 sparse backend is unavailable: %s" % exc) from exc
+    if capability // 10 != 10:
+        raise SparseSageError("B200 sparse backend requires sm_100; device is sm_%d" % capability)
+    return capability
+
+
+class B200SparseBackend:
+    name = "b200_sparse"
+    requires_registered_sage = False
+    requires_runtime_context = True
+    approximate = True
+
+    def __init__(self, config=None, *, router=None, projector=None, smooth_k=True, check_device=True):
+        self.config = config or HybridSparseConfig()
+        if not isinstance(self.config, HybridSparseConfig):
+            raise TypeError("config must be HybridSparseConfig")
+        if check_device:
+            preflight()
+        self.router = router if router is not None else SparseTileRouter(self.config)
+        if (self.router.q_tile, self.router.kv_tile) != (Q_TILE, KV_TILE):
+            raise SparseSageError(
+                "router geometry %dQ x %dKV does not match the kernel's %dQ x %dKV"
+                % (self.router.q_tile, self.router.kv_tile, Q_TILE, KV_TILE)
+            )
+        self.projector = projector
+        if self.config.mode == MODE_SAGE128_FUSED_QKV and self.projector is None:
+            from .projector import ChunkedSparseQKVProjector
+
+            self.projector = ChunkedSparseQKVProjector()
+        self.smooth_k = bool(smooth_k)
+        self._status = None
+
+    # -- identity ---------------------------------------------------------
+
+    @property
+    def installation_signature(self):
+        projector = self.projector
+        return (
+            self.name,
+            self.config.signature,
+            (type(self.router).__module__, type(self.router).__qualname__),
+            ("sm_100a", Q_TILE, KV_TILE, "int8_qk", "fp8_e4m3_v", V_QUANT_BOUND, _native.ABI_VERSION),
+            bool(self.smooth_k),
+            None
+            if projector is None
+            else (
+                type(projector).__module__,
+                type(projector).__qualname__,
+                getattr(projector, "name", None),
+                getattr(projector, "installation_signature", None),
+            ),
+        )
+
+    def as_status(self):
+        return {
+            "mode": self.config.mode,
+            "video_budget": float(self.config.video_budget),
+            "denser_early_late_steps": bool(self.config.denser_early_late_steps),
+            "density_mode": self.config.density_mode,
+            "sparge_attention": "h3sparse-abi-%d" % _native.ABI_VERSION,
+            "sparse_architecture": "sm_100a",
+            "sparse_q_tile": Q_TILE,
+            "sparse_kv_tile": KV_TILE,
+            "sparse_v_format": "fp8",
+            "sparse_v_quant_bound": V_QUANT_BOUND,
+            "sparse_extension_layout": "h3sparse",
+            "approximate": True,
+            "fused_qkv": self.projector is not None,
+            "qkv_projector": getattr(self.projector, "name", None),
+            "qkv_chunk_rows": getattr(self.projector, "chunk_rows", None),
+            "smooth_k": bool(self.smooth_k),
+        }
+
+    # -- helpers ------------------------------------------------------------
+
+    @staticmethod
+    def _snapshot(transformer_options, sequence):
+        snapshot = get_runtime_snapshot(transformer_options)
+        if snapshot is None:
+            raise SparseSageError("Sparse Attention requires an H3 runtime snapshot")
+        if not snapshot.valid_layout:
+            raise SparseSageError(
+                "Sparse Attention requires a valid packed layout: %s"
+                % (getattr(snapshot, "error", None) or "layout unavailable")
+            )
+        if int(snapshot.layout.seq_len) != int(sequence):
+            raise SparseSageError(
+                "runtime layout sequence %d does not match attention sequence %d"
+                % (snapshot.layout.seq_len, sequence)
+            )
+        return snapshot
+
+    @staticmethod
+    def _metadata(mask_metadata, layer_index, heads):
+        metadata = mask_metadata.as_dict()
+        metadata.update(
+            {
+                "layer": int(layer_index),
+                "sparse_sage_heads": int(heads),
+                "total_q_video_tiles": int(mask_metadata.pure_video_q_tiles) * int(heads),
+                "sparse_architecture": "sm_100a",
+                "sparse_q_tile": Q_TILE,
+                "sparse_kv_tile": KV_TILE,
+                "sparse_v_format": "fp8",
+                "sparse_accumulator": "f32",
+                "sparse_v_quant_bound": V_QUANT_BOUND,
+            }
+        )
+        return metadata
+
+    @staticmethod
+    def _sink(transformer_options, layer_index):
+        recorder = (transformer_options or {}).get("h3_optimizations_attention_route")
+        sink = getattr(recorder, "sink", None)
+        return {} if sink is None else {"sink": sink(layer_index)}
+
+    @staticmethod
+    def _validate_qkv(q, k, v):
+        if q.shape != k.shape or q.shape != v.shape:
+            raise SparseSageError(
+                "Sparse Sage requires equal self-attention Q/K/V shapes; got %s %s %s"
+                % (tuple(q.shape), tuple(k.shape), tuple(v.shape))
+            )
+        if q.ndim != 4:
+            raise SparseSageError("Sparse Sage expects HND rank-4 tensors")
+        batch, heads, sequence, head_dim = q.shape
+        if batch != 1:
+            raise SparseSageError("released H3 expects attention batch 1; got %d" % batch)
+        if head_dim != 128:
+            raise SparseSageError("Sparse Sage requires head_dim 128; got %d" % head_dim)
+        if q.dtype not in (torch.float16, torch.bfloat16, torch.float32) or q.dtype != k.dtype or q.dtype != v.dtype:
+            raise SparseSageError("Sparse Sage Q/K/V require matching fp16, bf16 or fp32 dtypes")
+        if q.device != k.device or q.device != v.device:
+            raise SparseSageError("Sparse Sage Q/K/V devices differ")
+        if any(t.stride(-1) != 1 for t in (q, k, v)):
+            raise SparseSageError("Sparse Sage Q/K/V last dimension must be contiguous")
+        if not q.is_cuda:
+            raise SparseSageError("Sparse Sage requires CUDA")
+        return heads, sequence
+
+    # -- protocol -------------------------------------------------------------
+
+    def prepare(self, q, k, v, *, layer_index, transformer_options):
+        heads, sequence = self._validate_qkv(q, k, v)
+        snapshot = self._snapshot(transformer_options, sequence)
+        video_budget = resolve_video_budget(
+            self.config, snapshot.step_index, snapshot.total_steps, layer_index
+        )
+        try:
+            geometry = self.router.geometry(snapshot.layout)
+            retained = self.router._retained(video_budget, geometry)
+            need_route = retained < geometry.pure_video_kv_tiles
+            summary_dtype = torch.float64 if need_route else None
+            k_mean, v_scale = ops.column_stats(k if self.smooth_k else None, v, V_QUANT_BOUND)
+            q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
+            k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
+            v_carrier, v_scale = ops.quant_v_fp8(v, v_scale, V_QUANT_BOUND)
+            if need_route:
+                route = self.router.build_route_from_summaries(
+                    q_summary, k_summary, snapshot.layout, video_budget,
+                    **self._sink(transformer_options, layer_index),
+                )
+            else:
+                route = self.router.build_route(
+                    q, k, snapshot.layout, video_budget, **self._sink(transformer_options, layer_index)
+                )
+        except SparseRouterError as exc:
+            raise SparseSageError("sparse routing failed: %s" % exc) from exc
+        except _native.NativeError as exc:
+            raise SparseSageError("carrier preparation failed: layer=%d: %s" % (layer_index, exc)) from exc
+        sparse = PreparedSparse(
+            q_int8=q_int8, k_int8=k_int8, v_carrier=v_carrier, q_scale=q_scale, k_scale=k_scale,
+            v_scale=v_scale, route=route, output_dtype=q.dtype, output_shape=tuple(q.shape),
+            layer_index=int(layer_index), sequence=int(sequence), heads=int(heads),
+            metadata=self._metadata(route.metadata, layer_index, heads),
+        )
+        sparse.metadata["smooth_k"] = bool(self.smooth_k)
+        return PreparedHybrid(sparse=sparse)
+
+    def prepare_projected(self, projected, *, layer_index, transformer_options):
+        try:
+            validate_prepared_fused_qkv(projected)
+        except FusedQKVError as exc:
+            raise SparseSageError(str(exc)) from exc
+        snapshot = self._snapshot(transformer_options, projected.sequence)
+        video_budget = resolve_video_budget(
+            self.config, snapshot.step_index, snapshot.total_steps, layer_index
+        )
+        heads, sequence = int(projected.heads), int(projected.sequence)
+        if not projected.q_int8.is_cuda:
+            raise SparseSageError("fused H3 Sparse Sage requires CUDA")
+        try:
+            route = self.router.build_route_from_summaries(
+                projected.q_summary, projected.k_summary, snapshot.layout, video_budget,
+                **self._sink(transformer_options, layer_index),
+            )
+            if projected.v_carrier is not None:
+                v_carrier, v_scale = projected.v_carrier, projected.v_scale
+            else:
+                v_carrier, v_scale = ops.quant_v_fp8(projected.v, None, V_QUANT_BOUND)
+        except SparseRouterError as exc:
+            raise SparseSageError("sparse routing failed: %s" % exc) from exc
+        except _native.NativeError as exc:
+            raise SparseSageError("carrier preparation failed: layer=%d: %s" % (layer_index, exc)) from exc
+        metadata = self._metadata(route.metadata, layer_index, heads)
+        metadata.update(
+            {
+                "qkv_projection": "fused_int8",
+                "smooth_k": bool(projected.smooth_k),
+                "prepacked_fp8_v": projected.v_carrier is not None,
+            }
+        )
+        sparse = PreparedSparse(
+            q_int8=projected.q_int8, k_int8=projected.k_int8, v_carrier=v_carrier,
+            q_scale=projected.q_scale, k_scale=projected.k_scale, v_scale=v_scale, route=route,
+            output_dtype=projected.output_dtype, output_shape=(1, heads, sequence, projected.head_dim),
+            layer_index=int(projected.layer_index), sequence=sequence, heads=heads, metadata=metadata,
+        )
+        return PreparedHybrid(sparse=sparse)
+
+    def execute(self, prepared):
+        sparse = prepared.sparse
+        route = sparse.route
+        geometry = route.geometry
+        try:
+            out_dtype = sparse.output_dtype
+            return ops.sparse_attention(
+                sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale,
+                sparse.v_scale, route.indices,
+                q_start=geometry.pure_video_q_start, q_stop=geometry.pure_video_q_stop,
+                out_dtype=out_dtype,
+            )
+        except _native.NativeError as exc:
+            raise SparseSageError(
+                "Sparse attention kernel failed: layer=%d sequence=%d heads=%d dtype=%s: %s"
+                % (sparse.layer_index, sparse.sequence, sparse.heads, sparse.output_dtype, exc)
+            ) from exc
+
+    def reference_lut(self, prepared):
+        """The route in the reference's delta-LUT encoding ``(lut, valid)``."""
+        sparse = prepared.sparse
+        lut, valid, _ = self.router._lut(sparse.route, sparse.q_int8.device, sparse.heads)
+        return lut, valid

@@ -1,0 +1,495 @@
+// Block-sparse attention on the INT8 Q/K + FP8 V carriers for sm_100a.
+//
+// One CTA owns one 128-row query tile of one head and walks that tile's list
+// of 64-row KV tiles:
+//   S = Q8 . K8^T      tcgen05.mma kind::i8, 128x64x128, int32 in TMEM (2 buffers)
+//   P = exp2(c*S - m)  FP32 in registers, one thread per query row, m an integer
+//                      so every rescale is an exact power of two
+//   O += P8 . V8       tcgen05.mma kind::f8f6f4, 128x128x64, fp32 in TMEM
+// P is carried as two E4M3 terms (hi = P rounded to 4 significant bits,
+// lo = E4M3(P - hi)) and the product is issued once per term, which gives the
+// probabilities ~7 significant bits; a single-term mode (flag
+// H3S_ATTN_P_SINGLE) trades that precision for fewer MMAs.
+// Warp roles: warps 0-3 softmax/epilogue (TMEM lanes 32w..32w+31), warp 4
+// TMA producer (K tile + V^T tile per stage, only the listed tiles are ever
+// fetched), warp 5 MMA issuer and TMEM owner.  Two CTAs share an SM
+// (2 x 256 TMEM columns, 2 x ~98 KB shared memory), so one CTA's softmax
+// overlaps the other's MMAs.
+//
+// O is rescaled lazily: the running maximum is only raised when a tile's
+// maximum exceeds it by more than 8 (P then stays <= 2^8 < 448 = E4M3 max).
+#include <climits>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tma.cuh"
+
+namespace h3s {
+
+constexpr int kStages = 3;
+constexpr int kAttnThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr uint32_t kQBytes = H3S_Q_TILE * H3S_HEAD_DIM;        // 16384
+constexpr uint32_t kKBytes = H3S_KV_TILE * H3S_HEAD_DIM;       // 8192
+constexpr uint32_t kVBytes = H3S_HEAD_DIM * H3S_KV_TILE;       // 8192
+constexpr uint32_t kPBytes = H3S_Q_TILE * H3S_KV_TILE;         // 8192
+constexpr uint32_t kOffQ = 0;
+constexpr uint32_t kOffK = kOffQ + kQBytes;
+constexpr uint32_t kOffV = kOffK + kStages * kKBytes;
+constexpr uint32_t kOffP = kOffV + kStages * kVBytes;
+constexpr uint32_t kOffBar = kOffP + 4 * kPBytes;  // P[buffer][hi|lo]
+constexpr uint32_t kAttnSmemBytes = kOffBar + 1024 + 1024;  // barriers/scalars + alignment slack
+// P = exp2(logit - m) with m = ceil(rowmax) - kPOffset when m is (re)set, so the
+// largest probability starts in (16, 32]; m is raised again only when a tile
+// would push P past 2^8 = 256 (E4M3 max 448).  The offset keeps small
+// probabilities and the lo term above the E4M3 underflow threshold (2^-9).
+constexpr float kRescaleThreshold = 8.0f;
+constexpr float kPOffset = 5.0f;
+
+enum AbortCode {
+  kAbortQFull = 1, kAbortKvFull, kAbortKvEmpty, kAbortSFull, kAbortSEmpty, kAbortPFull, kAbortPEmpty,
+  kAbortPvDone, kAbortFinal
+};
+
+struct AttnParams {
+  const float *q_scale;
+  const float *k_scale;
+  const float *v_scale;
+  const int32_t *route;  // (heads, q_stop-q_start, route_len) or null
+  void *out;
+  int32_t *status;
+  int64_t out_stride_h, out_stride_s;
+  int route_len, q_start, q_stop;
+  int heads, sequence, q_tiles, kv_tiles;
+  int out_dtype;
+};
+
+struct AttnShared {
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t s_empty[2];
+  uint64_t p_full[2];
+  uint64_t p_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+  float v_scale[H3S_HEAD_DIM];
+};
+static_assert(sizeof(AttnShared) <= 1024, "barrier block too large");
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Every lane polls the barrier; the warp then agrees on the outcome so that
+// the .sync.aligned tcgen05 instructions that follow stay convergent even if
+// the abort word was raised between two lanes' polls.
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word, int code) {
+  const bool ok = ptx::mbar_wait(bar, parity, abort_word, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
+  return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+template <typename OutT> __device__ __forceinline__ void store_out8(OutT *dst, const float (&v)[8]);
+template <> __device__ __forceinline__ void store_out8<float>(float *dst, const float (&v)[8]) {
+  reinterpret_cast<float4 *>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4 *>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void store_out8<__nv_bfloat16>(__nv_bfloat16 *dst, const float (&v)[8]) {
+  uint4 w;
+  __nv_bfloat162 t;
+  t = __floats2bfloat162_rn(v[0], v[1]); w.x = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2bfloat162_rn(v[2], v[3]); w.y = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2bfloat162_rn(v[4], v[5]); w.z = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2bfloat162_rn(v[6], v[7]); w.w = *reinterpret_cast<uint32_t *>(&t);
+  *reinterpret_cast<uint4 *>(dst) = w;
+}
+template <> __device__ __forceinline__ void store_out8<__half>(__half *dst, const float (&v)[8]) {
+  uint4 w;
+  __half2 t;
+  t = __floats2half2_rn(v[0], v[1]); w.x = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2half2_rn(v[2], v[3]); w.y = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2half2_rn(v[4], v[5]); w.z = *reinterpret_cast<uint32_t *>(&t);
+  t = __floats2half2_rn(v[6], v[7]); w.w = *reinterpret_cast<uint32_t *>(&t);
+  *reinterpret_cast<uint4 *>(dst) = w;
+}
+
+template <typename OutT, bool kSplitP>
+__global__ void __launch_bounds__(kAttnThreads, 2)
+sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                      const __grid_constant__ CUtensorMap map_v, const AttnParams prm) {
+  extern __shared__ unsigned char smem_dyn[];
+  // SWIZZLE_128B tiles need 1024-byte alignment
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+  AttnShared &sh = *reinterpret_cast<AttnShared *>(smem + kOffBar);
+  volatile int *abort_word = &sh.abort_word;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // ---- work item: dense (long) rows first, then the routed rows ----
+  const int n_sparse = prm.route != nullptr ? prm.q_stop - prm.q_start : 0;
+  const int n_dense = prm.q_tiles - n_sparse;
+  int head, tq;
+  bool dense;
+  {
+    const int w = blockIdx.x;
+    const int dense_items = prm.heads * n_dense;
+    if (w < dense_items) {
+      dense = true;
+      head = w / n_dense;
+      const int i = w - head * n_dense;
+      tq = (n_sparse == 0 || i < prm.q_start) ? i : prm.q_stop + (i - prm.q_start);
+    } else {
+      dense = false;
+      const int v = w - dense_items;
+      head = v / n_sparse;
+      tq = prm.q_start + (v - head * n_sparse);
+    }
+  }
+  const int n_iter = dense ? prm.kv_tiles : prm.route_len;
+  const int32_t *route_row =
+      dense ? nullptr
+            : prm.route + (static_cast<int64_t>(head) * n_sparse + (tq - prm.q_start)) * prm.route_len;
+
+  // ---- setup ----
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&sh.q_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      ptx::mbar_init(&sh.kv_full[i], 1);
+      ptx::mbar_init(&sh.kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&sh.s_full[i], 1);
+      ptx::mbar_init(&sh.s_empty[i], 4);
+      ptx::mbar_init(&sh.p_full[i], 4);
+      ptx::mbar_init(&sh.p_empty[i], 1);
+    }
+    sh.abort_word = 0;
+    ptx::fence_mbar_init();
+  }
+  if (threadIdx.x < H3S_HEAD_DIM) sh.v_scale[threadIdx.x] = __ldg(prm.v_scale + head * H3S_HEAD_DIM + threadIdx.x);
+  if (warp == 5) {
+    ptx::tmem_alloc(&sh.tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+  const uint32_t tmem_s = tmem_base;          // 2 x 64 columns, int32
+  const uint32_t tmem_o = tmem_base + 128;    // 128 columns, fp32
+
+  if (warp == 4) {
+    // =================== TMA producer ===================
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_q);
+      ptx::prefetch_tensormap(&map_k);
+      ptx::prefetch_tensormap(&map_v);
+      ptx::mbar_arrive_expect_tx(&sh.q_full, kQBytes);
+      ptx::tma_load_3d(smem + kOffQ, &map_q, &sh.q_full, 0, tq * H3S_Q_TILE, head);
+      for (int j = 0; j < n_iter; ++j) {
+        const int s = j % kStages;
+        const uint32_t use = static_cast<uint32_t>(j / kStages);
+        if (!ptx::mbar_wait(&sh.kv_empty[s], (use & 1u) ^ 1u, abort_word, kAbortKvEmpty)) break;
+        const int t = dense ? j : __ldg(route_row + j);
+        ptx::mbar_arrive_expect_tx(&sh.kv_full[s], kKBytes + kVBytes);
+        ptx::tma_load_3d(smem + kOffK + s * kKBytes, &map_k, &sh.kv_full[s], 0, t * H3S_KV_TILE, head);
+        ptx::tma_load_3d(smem + kOffV + s * kVBytes, &map_v, &sh.kv_full[s], t * H3S_KV_TILE, 0, head);
+      }
+    }
+  } else if (warp == 5) {
+    // =================== MMA issuer ===================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::umma_idesc(2, 1, 1, H3S_Q_TILE, H3S_KV_TILE);
+      constexpr uint32_t idesc_pv = ptx::umma_idesc(1, 0, 0, H3S_Q_TILE, H3S_HEAD_DIM);
+      const uint32_t q_addr = ptx::smem_u32(smem + kOffQ);
+      bool ok = ptx::mbar_wait(&sh.q_full, 0, abort_word, kAbortQFull);
+      for (int j = 0; ok && j <= n_iter; ++j) {
+        if (j < n_iter) {
+          const int s = j % kStages, b = j & 1;
+          const uint32_t kv_use = static_cast<uint32_t>(j / kStages), s_use = static_cast<uint32_t>(j >> 1);
+          if (!ptx::mbar_wait(&sh.kv_full[s], kv_use & 1u, abort_word, kAbortKvFull)) { ok = false; break; }
+          if (!ptx::mbar_wait(&sh.s_empty[b], (s_use & 1u) ^ 1u, abort_word, kAbortSEmpty)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t a_desc = ptx::umma_desc_kmajor(q_addr, 1024, ptx::kSwizzle128);
+          const uint64_t b_desc =
+              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffK + s * kKBytes), 1024, ptx::kSwizzle128);
+#pragma unroll
+          for (int k = 0; k < H3S_HEAD_DIM / 32; ++k)
+            ptx::umma_i8(tmem_s + b * H3S_KV_TILE, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, k > 0);
+          ptx::tc_commit(&sh.s_full[b]);
+        }
+        if (j > 0) {
+          const int i = j - 1;
+          const int s = i % kStages, b = i & 1;
+          const uint32_t p_use = static_cast<uint32_t>(i >> 1);
+          if (!ptx::mbar_wait(&sh.p_full[b], p_use & 1u, abort_word, kAbortPFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t b_desc =
+              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV + s * kVBytes), 512, ptx::kSwizzle64);
+#pragma unroll
+          for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
+            const uint64_t a_desc = ptx::umma_desc_kmajor(
+                ptx::smem_u32(smem + kOffP + (2 * b + term) * kPBytes), 512, ptx::kSwizzle64);
+#pragma unroll
+            for (int k = 0; k < H3S_KV_TILE / 32; ++k)
+              ptx::umma_f8(tmem_o, a_desc + 2 * k, b_desc + 2 * k, idesc_pv,
+                           (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(&sh.kv_empty[s]);
+          ptx::tc_commit(&sh.p_empty[b]);
+        }
+      }
+    }
+  } else {
+    // =================== softmax + epilogue (warps 0-3) ===================
+    const int row = warp * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    const float q_scale = __ldg(prm.q_scale + head * prm.q_tiles + tq) * (0.08838834764831845f * 1.4426950408889634f);
+    const float *k_scale = prm.k_scale + static_cast<int64_t>(head) * prm.kv_tiles;
+    unsigned char *p_row = smem + kOffP + row * H3S_KV_TILE;  // + (2*buffer + term) * kPBytes
+    const int swz = (row >> 1) & 3;
+    float m_used = -INFINITY;
+    float l = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_iter; ++j) {
+      const int b = j & 1;
+      const uint32_t use = static_cast<uint32_t>(j >> 1);
+      if (!warp_wait(&sh.s_full[b], use & 1u, abort_word, kAbortSFull)) { ok = false; break; }
+      ptx::tc_fence_after();
+      uint32_t s[64];
+      H3S_TMEM_LD32(tmem_s + lane_addr + b * H3S_KV_TILE, s);
+      {
+        uint32_t *s_hi = s + 32;
+        H3S_TMEM_LD32(tmem_s + lane_addr + b * H3S_KV_TILE + 32, s_hi);
+      }
+      ptx::tmem_wait_ld();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&sh.s_empty[b]);
+
+      const int t = dense ? j : __ldg(route_row + j);
+      const float c = q_scale * __ldg(k_scale + t);
+      const int n_valid = min(H3S_KV_TILE, prm.sequence - t * H3S_KV_TILE);
+
+      int imax = INT_MIN;
+      if (n_valid == H3S_KV_TILE) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) imax = max(imax, static_cast<int>(s[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (i < n_valid) imax = max(imax, static_cast<int>(s[i]));
+      }
+      const float mx = c * static_cast<float>(imax);
+      const bool need = mx > m_used + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_new = need ? ceilf(mx) - kPOffset : m_used;
+        const float alpha = fast_exp2(m_used - m_new);  // 1 when unchanged, 0 from -inf
+        if (j > 0) {
+          const int pb = (j - 1) & 1;
+          const uint32_t pu = static_cast<uint32_t>((j - 1) >> 1);
+          if (!warp_wait(&sh.p_empty[pb], pu & 1u, abort_word, kAbortPvDone)) { ok = false; break; }
+          ptx::tc_fence_after();
+#pragma unroll 1
+          for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+            uint32_t o[32];
+            H3S_TMEM_LD32(tmem_o + lane_addr + cc * 32, o);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            H3S_TMEM_ST32(tmem_o + lane_addr + cc * 32, o);
+          }
+          ptx::tmem_wait_st();
+          ptx::tc_fence_before();
+        }
+        l *= alpha;
+        m_used = m_new;
+      }
+
+      float sum = 0.f;
+      uint32_t packed[16];
+      uint32_t packed_lo[kSplitP ? 16 : 1];
+#pragma unroll
+      for (int i = 0; i < 64; i += 4) {
+        float p[4], r[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          p[e] = fast_exp2(fmaf(c, static_cast<float>(static_cast<int>(s[i + e])), -m_used));
+          if (i + e >= n_valid) p[e] = 0.f;
+          sum += p[e];
+          if (kSplitP) {
+            // hi keeps 4 significant bits (exactly representable in E4M3), lo is the remainder
+            const float hi = __uint_as_float((__float_as_uint(p[e]) + 0x00080000u) & 0xfff00000u);
+            r[e] = p[e] - hi;
+            p[e] = hi;
+          }
+        }
+        packed[i >> 2] = pack_e4m3x4(p[0], p[1], p[2], p[3]);
+        if (kSplitP) packed_lo[i >> 2] = pack_e4m3x4(r[0], r[1], r[2], r[3]);
+      }
+      l += sum;
+
+      if (!warp_wait(&sh.p_empty[b], (use & 1u) ^ 1u, abort_word, kAbortPEmpty)) { ok = false; break; }
+      unsigned char *dst = p_row + 2 * b * kPBytes;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        *reinterpret_cast<uint4 *>(dst + ((ch ^ swz) << 4)) =
+            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+        if (kSplitP)
+          *reinterpret_cast<uint4 *>(dst + kPBytes + ((ch ^ swz) << 4)) = make_uint4(
+              packed_lo[4 * ch], packed_lo[4 * ch + 1], packed_lo[4 * ch + 2], packed_lo[4 * ch + 3]);
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&sh.p_full[b]);
+    }
+
+    if (ok) {
+      const int last = n_iter - 1;
+      ok = warp_wait(&sh.p_empty[last & 1], static_cast<uint32_t>(last >> 1) & 1u, abort_word, kAbortFinal);
+    }
+    if (ok) {
+      ptx::tc_fence_after();
+      const float inv_l = 1.0f / l;
+      const int grow = tq * H3S_Q_TILE + row;
+      OutT *orow = static_cast<OutT *>(prm.out) + head * prm.out_stride_h +
+                   static_cast<int64_t>(grow) * prm.out_stride_s;
+#pragma unroll 1
+      for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+        uint32_t o[32];
+        H3S_TMEM_LD32(tmem_o + lane_addr + cc * 32, o);
+        ptx::tmem_wait_ld();
+        if (grow < prm.sequence) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              v[e] = __uint_as_float(o[i + e]) * sh.v_scale[cc * 32 + i + e] * inv_l;
+            store_out8<OutT>(orow + cc * 32 + i, v);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+    }
+  }
+
+  // ---- teardown ----
+  __syncthreads();
+  const int code = sh.abort_word;
+  if (code != 0) {
+    // leave time for copies / MMAs still in flight before releasing TMEM and shared memory
+    __nanosleep(200000);
+    if (threadIdx.x == 0 && prm.status != nullptr) {
+      if (atomicCAS(prm.status, 0, code) == 0) {
+        prm.status[1] = blockIdx.x;
+        prm.status[2] = head;
+        prm.status[3] = tq;
+      }
+    }
+  }
+  if (warp == 5) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <typename OutT, bool kSplitP>
+static int launch_attn_tc_impl(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
+                               const AttnParams &prm, cudaStream_t stream) {
+  H3S_CHECK_CUDA(cudaFuncSetAttribute(sparse_attn_tc_kernel<OutT, kSplitP>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kAttnSmemBytes)));
+  const int grid = prm.heads * prm.q_tiles;
+  sparse_attn_tc_kernel<OutT, kSplitP><<<grid, kAttnThreads, kAttnSmemBytes, stream>>>(mq, mk, mv, prm);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+template <typename OutT>
+static int launch_attn_tc(const CUtensorMap &mq, const CUtensorMap &mk, const CUtensorMap &mv,
+                          const AttnParams &prm, bool split_p, cudaStream_t stream) {
+  return split_p ? launch_attn_tc_impl<OutT, true>(mq, mk, mv, prm, stream)
+                 : launch_attn_tc_impl<OutT, false>(mq, mk, mv, prm, stream);
+}
+
+int check_attn_args(const int8_t *q8, const int8_t *k8, const uint8_t *v8t, const float *q_scale,
+                    const float *k_scale, const float *v_scale, const int32_t *route, int route_len,
+                    int q_start, int q_stop, void *out, int out_dtype, int64_t out_stride_h,
+                    int64_t out_stride_s, int heads, int sequence, const char *who) {
+  H3S_CHECK_ARG(q8 && k8 && v8t && q_scale && k_scale && v_scale && out, "%s: NULL pointer", who);
+  H3S_CHECK_ARG(heads > 0 && sequence > 0, "%s: empty problem (heads=%d sequence=%d)", who, heads, sequence);
+  H3S_CHECK_ARG(out_dtype == H3S_F32 || out_dtype == H3S_BF16 || out_dtype == H3S_F16, "%s: bad out dtype %d", who, out_dtype);
+  const int vec = out_dtype == H3S_F32 ? 4 : 8;
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 15) == 0 && out_stride_h % vec == 0 && out_stride_s % vec == 0 && out_stride_s >= H3S_HEAD_DIM,
+                "%s: output must be 16-byte aligned with strides that are multiples of %d elements", who, vec);
+  H3S_CHECK_ARG(((reinterpret_cast<uintptr_t>(q8) | reinterpret_cast<uintptr_t>(k8) | reinterpret_cast<uintptr_t>(v8t)) & 15) == 0,
+                "%s: carriers must be 16-byte aligned", who);
+  const int q_tiles = ceil_div(sequence, H3S_Q_TILE), kv_tiles = ceil_div(sequence, H3S_KV_TILE);
+  if (route != nullptr) {
+    H3S_CHECK_ARG(0 <= q_start && q_start < q_stop && q_stop <= q_tiles, "%s: bad routed query range [%d,%d) of %d", who, q_start, q_stop, q_tiles);
+    H3S_CHECK_ARG(route_len >= 1 && route_len <= kv_tiles, "%s: route_len %d outside [1,%d]", who, route_len, kv_tiles);
+  }
+  return H3S_OK;
+}
+
+}  // namespace h3s
+
+extern "C" int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
+                                   const float *q_scale, const float *k_scale, const float *v_scale,
+                                   const int32_t *route, int route_len, int q_start, int q_stop,
+                                   void *out, int out_dtype, int64_t out_stride_h, int64_t out_stride_s,
+                                   int heads, int sequence, int flags, int32_t *status,
+                                   h3s_stream_t stream) {
+  using namespace h3s;
+  {
+    int rc = check_attn_args(q8, k8, v8t, q_scale, k_scale, v_scale, route, route_len, q_start, q_stop, out,
+                             out_dtype, out_stride_h, out_stride_s, heads, sequence, "sparse_attn_fwd");
+    if (rc) return rc;
+  }
+  const int cap = h3s_device_capability();
+  if (cap < 0) return cap;
+  if (cap / 10 != 10) return fail(H3S_EARCH, "sparse_attn_fwd: needs an sm_100 device, found sm_%d", cap);
+
+  const uint64_t S = static_cast<uint64_t>(sequence);
+  const uint64_t padded = static_cast<uint64_t>(ceil_div(sequence, 128)) * 128;
+  CUtensorMap mq, mk, mv;
+  int rc = make_tensor_map_u8_3d(&mq, q8, H3S_HEAD_DIM, S, heads, H3S_HEAD_DIM, S * H3S_HEAD_DIM,
+                                 H3S_HEAD_DIM, H3S_Q_TILE, CU_TENSOR_MAP_SWIZZLE_128B, "sparse_attn_fwd Q map");
+  if (rc) return rc;
+  rc = make_tensor_map_u8_3d(&mk, k8, H3S_HEAD_DIM, S, heads, H3S_HEAD_DIM, S * H3S_HEAD_DIM, H3S_HEAD_DIM,
+                             H3S_KV_TILE, CU_TENSOR_MAP_SWIZZLE_128B, "sparse_attn_fwd K map");
+  if (rc) return rc;
+  rc = make_tensor_map_u8_3d(&mv, v8t, padded, H3S_HEAD_DIM, heads, padded, padded * H3S_HEAD_DIM,
+                             H3S_KV_TILE, H3S_HEAD_DIM, CU_TENSOR_MAP_SWIZZLE_64B, "sparse_attn_fwd V map");
+  if (rc) return rc;
+
+  AttnParams prm;
+  prm.q_scale = q_scale; prm.k_scale = k_scale; prm.v_scale = v_scale;
+  prm.route = route; prm.out = out; prm.status = status;
+  prm.out_stride_h = out_stride_h; prm.out_stride_s = out_stride_s;
+  prm.route_len = route_len; prm.q_start = q_start; prm.q_stop = q_stop;
+  prm.heads = heads; prm.sequence = sequence;
+  prm.q_tiles = ceil_div(sequence, H3S_Q_TILE); prm.kv_tiles = ceil_div(sequence, H3S_KV_TILE);
+  prm.out_dtype = out_dtype;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool split_p = (flags & H3S_ATTN_P_SINGLE) == 0;
+  switch (out_dtype) {
+    case H3S_F32: return launch_attn_tc<float>(mq, mk, mv, prm, split_p, s);
+    case H3S_BF16: return launch_attn_tc<__nv_bfloat16>(mq, mk, mv, prm, split_p, s);
+    default: return launch_attn_tc<__half>(mq, mk, mv, prm, split_p, s);
+  }
+}

@@ -1,0 +1,90 @@
+// Shared host/device helpers for the h3sparse kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/h3sparse.h"
+
+namespace h3s {
+
+// Records the message returned by h3s_last_error() and returns `code`.
+int fail(int code, const char *fmt, ...);
+
+#define H3S_CHECK_ARG(cond, ...)                          \
+  do {                                                    \
+    if (!(cond)) return ::h3s::fail(H3S_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define H3S_CHECK_CUDA(expr)                                                   \
+  do {                                                                         \
+    cudaError_t err__ = (expr);                                                \
+    if (err__ != cudaSuccess)                                                  \
+      return ::h3s::fail(H3S_ECUDA, "%s failed: %s", #expr,                    \
+                         cudaGetErrorString(err__));                           \
+  } while (0)
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- element loads: 8 consecutive channels of one row, widened to fp32 ----
+
+template <typename T>
+struct Elem;
+
+template <>
+struct Elem<float> {
+  static constexpr int kDtype = H3S_F32;
+  __device__ static void load8(const float *p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+  __device__ static float round_trip(float x) { return x; }
+};
+
+template <>
+struct Elem<__nv_bfloat16> {
+  static constexpr int kDtype = H3S_BF16;
+  __device__ static void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ static float round_trip(float x) {
+    return __bfloat162float(__float2bfloat16_rn(x));
+  }
+};
+
+template <>
+struct Elem<__half> {
+  static constexpr int kDtype = H3S_F16;
+  __device__ static void load8(const __half *p, float (&v)[8]) {
+    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static float round_trip(float x) {
+    return __half2float(__float2half_rn(x));
+  }
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace h3s

@@ -1,0 +1,415 @@
+// Carrier quantisation kernels (HBM-bound): whole-sequence column statistics,
+// per-block INT8 Q/K with tile means, FP8-E4M3 transposed V.
+//
+// Thread mapping shared by all three: 16 consecutive threads read one
+// 128-channel row as 16-byte vectors (8 channels each), so a warp covers two
+// full rows and every global load/store is a fully used 128/256/512-byte line.
+#include "common.cuh"
+
+namespace h3s {
+
+// ---------------------------------------------------------------------------
+// Column statistics: sum_s K[h,s,d] (FP64) and max_s |V[h,s,d]|.
+// scratch layout: double k_sum[heads*128]; uint32 v_amax_bits[heads*128].
+// ---------------------------------------------------------------------------
+
+constexpr int kStatsThreads = 256;
+constexpr int kStatsRowsPerBlock = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(kStatsThreads)
+column_stats_kernel(const T *__restrict__ k, int64_t k_stride_h, int64_t k_stride_s,
+                    const T *__restrict__ v, int64_t v_stride_h, int64_t v_stride_s,
+                    int sequence, double *__restrict__ k_sum,
+                    unsigned int *__restrict__ v_amax_bits) {
+  __shared__ double red[kStatsThreads / 16][H3S_HEAD_DIM];
+  const int head = blockIdx.y;
+  const bool is_v = blockIdx.z == 1;
+  const T *src = is_v ? v : k;
+  if (src == nullptr) return;
+  const int64_t stride_h = is_v ? v_stride_h : k_stride_h;
+  const int64_t stride_s = is_v ? v_stride_s : k_stride_s;
+  const int slot = threadIdx.x >> 4;
+  const int c0 = (threadIdx.x & 15) * 8;
+  const int row_begin = blockIdx.x * kStatsRowsPerBlock;
+  const int row_end = min(row_begin + kStatsRowsPerBlock, sequence);
+  double acc[8];
+  float amax[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { acc[i] = 0.0; amax[i] = 0.f; }
+  const T *base = src + head * stride_h + c0;
+  for (int row = row_begin + slot; row < row_end; row += kStatsThreads / 16) {
+    float x[8];
+    Elem<T>::load8(base + row * stride_s, x);
+    if (is_v) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax[i] = fmaxf(amax[i], fabsf(x[i]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += static_cast<double>(x[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[slot][c0 + i] = is_v ? static_cast<double>(amax[i]) : acc[i];
+  __syncthreads();
+  if (threadIdx.x < H3S_HEAD_DIM) {
+    const int d = threadIdx.x;
+    if (is_v) {
+      double m = 0.0;
+#pragma unroll
+      for (int s = 0; s < kStatsThreads / 16; ++s) m = fmax(m, red[s][d]);
+      // non-negative floats order like their bit patterns
+      atomicMax(&v_amax_bits[head * H3S_HEAD_DIM + d], __float_as_uint(static_cast<float>(m)));
+    } else {
+      double s = 0.0;
+#pragma unroll
+      for (int i = 0; i < kStatsThreads / 16; ++i) s += red[i][d];
+      atomicAdd(&k_sum[head * H3S_HEAD_DIM + d], s);
+    }
+  }
+}
+
+template <typename T>
+__global__ void column_stats_finalize_kernel(const double *__restrict__ k_sum,
+                                             const unsigned int *__restrict__ v_amax_bits,
+                                             int total, int sequence, float v_bound,
+                                             float *__restrict__ k_mean,
+                                             float *__restrict__ v_scale) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  if (k_mean != nullptr) {
+    const float mean = static_cast<float>(k_sum[i] / static_cast<double>(sequence));
+    k_mean[i] = Elem<T>::round_trip(mean);
+  }
+  if (v_scale != nullptr) {
+    const float amax = __uint_as_float(v_amax_bits[i]);
+    v_scale[i] = fmaxf(__fdiv_rn(amax, v_bound), 1.0e-20f);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Per-block INT8 quantisation with optional tile means.
+// One CTA = one (block, head); the whole block lives in registers
+// (64 values per thread) between the amax reduction and the store.
+// ---------------------------------------------------------------------------
+
+template <typename T, int BLOCK>
+__global__ void __launch_bounds__(BLOCK * 2)
+quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride_s,
+                       const float *__restrict__ mean, int8_t *__restrict__ out,
+                       float *__restrict__ scale_out, void *__restrict__ summary,
+                       int summary_dtype, int rows, int row_start, int sequence_total,
+                       int blocks_total) {
+  constexpr int kThreads = BLOCK * 2;
+  constexpr int kSlots = kThreads / 16;  // rows per pass
+  constexpr int kPasses = BLOCK / kSlots;  // == 8
+  __shared__ float warp_amax[kThreads / 32];
+  __shared__ double red[kSlots][H3S_HEAD_DIM];
+
+  const int local_block = blockIdx.x;
+  const int head = blockIdx.y;
+  const int slot = threadIdx.x >> 4;
+  const int c0 = (threadIdx.x & 15) * 8;
+  const int first_row = local_block * BLOCK;  // within this chunk
+  const int valid_rows = min(BLOCK, rows - first_row);
+
+  float mu[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) mu[i] = 0.f;
+  if (mean != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mu[i] = __ldg(mean + head * H3S_HEAD_DIM + c0 + i);
+  }
+
+  float val[kPasses][8];
+  double col[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) col[i] = 0.0;
+  float amax = 0.f;
+  const T *base = x + head * stride_h + c0;
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int r = p * kSlots + slot;
+    if (r < valid_rows) {
+      float raw[8];
+      Elem<T>::load8(base + static_cast<int64_t>(first_row + r) * stride_s, raw);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        col[i] += static_cast<double>(raw[i]);
+        val[p][i] = __fsub_rn(raw[i], mu[i]);
+        amax = fmaxf(amax, fabsf(val[p][i]));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) val[p][i] = 0.f;
+    }
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x >> 5] = amax;
+  if (summary != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[slot][c0 + i] = col[i];
+  }
+  __syncthreads();
+  amax = warp_amax[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, warp_amax[w]);
+  const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 1.0e-7f);
+
+  const int global_block = row_start / BLOCK + local_block;
+  if (threadIdx.x == 0 && scale_out != nullptr) scale_out[head * blocks_total + global_block] = scale;
+
+  int8_t *dst = out + (static_cast<int64_t>(head) * sequence_total + row_start + first_row) *
+                          H3S_HEAD_DIM + c0;
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int r = p * kSlots + slot;
+    if (out != nullptr && r < valid_rows) {
+      uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float q = __fdiv_rn(val[p][i], scale);
+        q = __fadd_rn(q, q >= 0.f ? 0.5f : -0.5f);
+        const int code = static_cast<int>(q);  // truncation toward zero
+        packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+      }
+      *reinterpret_cast<uint2 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) =
+          make_uint2(packed[0], packed[1]);
+    }
+  }
+
+  if (summary != nullptr && threadIdx.x < H3S_HEAD_DIM) {
+    const int d = threadIdx.x;
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < kSlots; ++i) s += red[i][d];
+    const double m = s / static_cast<double>(valid_rows);
+    const int64_t at = (static_cast<int64_t>(head) * blocks_total + global_block) * H3S_HEAD_DIM + d;
+    switch (summary_dtype) {
+      case H3S_F64: static_cast<double *>(summary)[at] = m; break;
+      case H3S_F32: static_cast<float *>(summary)[at] = static_cast<float>(m); break;
+      case H3S_BF16:
+        static_cast<__nv_bfloat16 *>(summary)[at] = __float2bfloat16_rn(static_cast<float>(m));
+        break;
+      default:
+        static_cast<__half *>(summary)[at] = __float2half_rn(static_cast<float>(m));
+        break;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// FP8-E4M3 V carrier, transposed to (heads, 128, pad128(S)).
+// One CTA = 128 sequence rows of one head, staged through shared memory so
+// that both the row-major reads and the channel-major writes are full lines.
+// ---------------------------------------------------------------------------
+
+constexpr int kVTile = 128;
+constexpr int kVThreads = 256;
+
+// Shared tile: 128 channel rows of 128 bytes; the 16-byte chunk index of
+// channel row d is XORed with (d>>3)&7 so the transposing 4-byte stores of
+// the 16 lanes that share a sequence position fall in different banks.
+__device__ __forceinline__ int v_tile_offset(int d, int s) {
+  const int chunk = (s >> 4) ^ ((d >> 3) & 7);
+  return d * kVTile + chunk * 16 + (s & 15);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kVThreads)
+quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
+                   const float *__restrict__ v_scale, uint8_t *__restrict__ out, int rows,
+                   int row_start, int padded_total, float v_bound) {
+  __shared__ __align__(16) uint8_t tile[H3S_HEAD_DIM * kVTile];
+  const int head = blockIdx.y;
+  const int first_row = blockIdx.x * kVTile;
+  const int valid_rows = max(0, min(kVTile, rows - first_row));
+  const int slot = threadIdx.x >> 4;
+  const int c0 = (threadIdx.x & 15) * 8;
+
+  float sc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    sc[i] = fmaxf(__ldg(v_scale + head * H3S_HEAD_DIM + c0 + i), 1.0e-20f);
+
+  const T *base = v + head * stride_h + c0;
+#pragma unroll
+  for (int p = 0; p < kVTile / (kVThreads / 16 * 4); ++p) {
+    const int r0 = (p * (kVThreads / 16) + slot) * 4;  // four consecutive rows
+    uint32_t word[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) word[i] = 0u;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (r0 + j < valid_rows) {
+        float raw[8];
+        Elem<T>::load8(base + static_cast<int64_t>(first_row + r0 + j) * stride_s, raw);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float q = __fdiv_rn(raw[i], sc[i]);
+          q = fminf(fmaxf(q, -v_bound), v_bound);
+          const uint32_t code = __nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
+          word[i] |= (code & 0xffu) << (8 * j);
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<uint32_t *>(&tile[v_tile_offset(c0 + i, r0)]) = word[i];
+  }
+  __syncthreads();
+  uint8_t *dst = out + static_cast<int64_t>(head) * H3S_HEAD_DIM * padded_total + row_start + first_row;
+#pragma unroll
+  for (int p = 0; p < H3S_HEAD_DIM / (kVThreads / 8); ++p) {
+    const int d = p * (kVThreads / 8) + (threadIdx.x >> 3);
+    const int chunk = threadIdx.x & 7;
+    const uint4 data = *reinterpret_cast<const uint4 *>(&tile[v_tile_offset(d, chunk * 16)]);
+    *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(d) * padded_total + chunk * 16) = data;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+
+static int check_view(const void *p, int dtype, int64_t stride_h, int64_t stride_s, const char *what) {
+  const int vec = dtype == H3S_F32 ? 4 : 8;  // elements per 16 bytes
+  H3S_CHECK_ARG(dtype == H3S_F32 || dtype == H3S_BF16 || dtype == H3S_F16,
+                "%s: unsupported dtype %d", what, dtype);
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(p) & 15) == 0, "%s: pointer must be 16-byte aligned", what);
+  H3S_CHECK_ARG(stride_h % vec == 0 && stride_s % vec == 0 && stride_s >= H3S_HEAD_DIM,
+                "%s: strides (%lld,%lld) must be multiples of %d elements with row stride >= 128",
+                what, static_cast<long long>(stride_h), static_cast<long long>(stride_s), vec);
+  return H3S_OK;
+}
+
+template <typename T>
+static int launch_column_stats(const void *k, int64_t ksh, int64_t kss, const void *v, int64_t vsh,
+                               int64_t vss, int heads, int sequence, float v_bound, float *k_mean,
+                               float *v_scale, void *scratch, cudaStream_t stream) {
+  double *k_sum = static_cast<double *>(scratch);
+  unsigned int *v_bits = reinterpret_cast<unsigned int *>(k_sum + heads * H3S_HEAD_DIM);
+  H3S_CHECK_CUDA(cudaMemsetAsync(scratch, 0, h3s_column_stats_scratch_bytes(heads), stream));
+  dim3 grid(ceil_div(sequence, kStatsRowsPerBlock), heads, 2);
+  column_stats_kernel<T><<<grid, kStatsThreads, 0, stream>>>(
+      static_cast<const T *>(k), ksh, kss, static_cast<const T *>(v), vsh, vss, sequence, k_sum, v_bits);
+  const int total = heads * H3S_HEAD_DIM;
+  column_stats_finalize_kernel<T><<<ceil_div(total, 256), 256, 0, stream>>>(
+      k_sum, v_bits, total, sequence, v_bound, k == nullptr ? nullptr : k_mean,
+      v == nullptr ? nullptr : v_scale);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+template <typename T>
+static int launch_quant_qk(const void *x, int64_t sh, int64_t ss, const float *mean, int8_t *out,
+                           float *scale, void *summary, int summary_dtype, int heads, int rows,
+                           int row_start, int sequence_total, int block, cudaStream_t stream) {
+  const int blocks = ceil_div(rows, block);
+  const int blocks_total = ceil_div(sequence_total, block);
+  dim3 grid(blocks, heads);
+  if (block == H3S_Q_TILE) {
+    quant_qk_blocks_kernel<T, H3S_Q_TILE><<<grid, H3S_Q_TILE * 2, 0, stream>>>(
+        static_cast<const T *>(x), sh, ss, mean, out, scale, summary, summary_dtype, rows, row_start,
+        sequence_total, blocks_total);
+  } else {
+    quant_qk_blocks_kernel<T, H3S_KV_TILE><<<grid, H3S_KV_TILE * 2, 0, stream>>>(
+        static_cast<const T *>(x), sh, ss, mean, out, scale, summary, summary_dtype, rows, row_start,
+        sequence_total, blocks_total);
+  }
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+template <typename T>
+static int launch_quant_v(const void *v, int64_t sh, int64_t ss, const float *v_scale, uint8_t *out,
+                          int heads, int rows, int row_start, int sequence_total, float v_bound,
+                          cudaStream_t stream) {
+  const int padded_total = ceil_div(sequence_total, 128) * 128;
+  // the final chunk also writes the zero padding up to the carrier's end
+  const bool last = row_start + rows == sequence_total;
+  const int covered = last ? padded_total - row_start : rows;
+  dim3 grid(ceil_div(covered, kVTile), heads);
+  quant_v_fp8_kernel<T><<<grid, kVThreads, 0, stream>>>(static_cast<const T *>(v), sh, ss, v_scale, out,
+                                                        rows, row_start, padded_total, v_bound);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+}  // namespace h3s
+
+extern "C" {
+
+size_t h3s_column_stats_scratch_bytes(int heads) {
+  return static_cast<size_t>(heads) * H3S_HEAD_DIM * (sizeof(double) + sizeof(unsigned int));
+}
+
+int h3s_column_stats(const void *k, int64_t k_stride_h, int64_t k_stride_s, const void *v,
+                     int64_t v_stride_h, int64_t v_stride_s, int dtype, int heads, int sequence,
+                     float v_bound, float *k_mean, float *v_scale, void *scratch,
+                     h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(heads > 0 && sequence > 0, "column_stats: empty problem (heads=%d sequence=%d)", heads, sequence);
+  H3S_CHECK_ARG(k != nullptr || v != nullptr, "column_stats: both inputs are NULL");
+  H3S_CHECK_ARG(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 7) == 0,
+                "column_stats: scratch must be non-NULL and 8-byte aligned");
+  H3S_CHECK_ARG(k == nullptr || k_mean != nullptr, "column_stats: k given without k_mean");
+  H3S_CHECK_ARG(v == nullptr || (v_scale != nullptr && v_bound > 0.f), "column_stats: v given without v_scale/bound");
+  if (k != nullptr) { int rc = check_view(k, dtype, k_stride_h, k_stride_s, "column_stats k"); if (rc) return rc; }
+  if (v != nullptr) { int rc = check_view(v, dtype, v_stride_h, v_stride_s, "column_stats v"); if (rc) return rc; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case H3S_F32: return launch_column_stats<float>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
+    case H3S_BF16: return launch_column_stats<__nv_bfloat16>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
+    default: return launch_column_stats<__half>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
+  }
+}
+
+int h3s_quant_qk_blocks(const void *x, int dtype, int64_t x_stride_h, int64_t x_stride_s,
+                        const float *mean, int8_t *out, float *scale, void *summary,
+                        int summary_dtype, int heads, int rows, int row_start, int sequence_total,
+                        int block, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(block == H3S_Q_TILE || block == H3S_KV_TILE, "quant_qk_blocks: block must be 128 or 64, got %d", block);
+  H3S_CHECK_ARG(heads > 0 && rows > 0 && sequence_total > 0, "quant_qk_blocks: empty problem");
+  H3S_CHECK_ARG(row_start >= 0 && row_start % block == 0, "quant_qk_blocks: row_start %d is not a multiple of the block %d", row_start, block);
+  H3S_CHECK_ARG(row_start + rows <= sequence_total, "quant_qk_blocks: chunk [%d,%d) exceeds sequence %d", row_start, row_start + rows, sequence_total);
+  H3S_CHECK_ARG(rows % block == 0 || row_start + rows == sequence_total,
+                "quant_qk_blocks: only the final chunk may contain a partial tile");
+  H3S_CHECK_ARG(x != nullptr, "quant_qk_blocks: NULL input");
+  H3S_CHECK_ARG((out != nullptr) == (scale != nullptr), "quant_qk_blocks: out and scale must be given together");
+  H3S_CHECK_ARG(out != nullptr || summary != nullptr, "quant_qk_blocks: nothing to produce");
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 7) == 0, "quant_qk_blocks: out must be 8-byte aligned");
+  H3S_CHECK_ARG(summary == nullptr || (summary_dtype >= H3S_F32 && summary_dtype <= H3S_F64),
+                "quant_qk_blocks: bad summary dtype %d", summary_dtype);
+  { int rc = check_view(x, dtype, x_stride_h, x_stride_s, "quant_qk_blocks x"); if (rc) return rc; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case H3S_F32: return launch_quant_qk<float>(x, x_stride_h, x_stride_s, mean, out, scale, summary, summary_dtype, heads, rows, row_start, sequence_total, block, s);
+    case H3S_BF16: return launch_quant_qk<__nv_bfloat16>(x, x_stride_h, x_stride_s, mean, out, scale, summary, summary_dtype, heads, rows, row_start, sequence_total, block, s);
+    default: return launch_quant_qk<__half>(x, x_stride_h, x_stride_s, mean, out, scale, summary, summary_dtype, heads, rows, row_start, sequence_total, block, s);
+  }
+}
+
+int h3s_quant_v_fp8(const void *v, int dtype, int64_t v_stride_h, int64_t v_stride_s,
+                    const float *v_scale, uint8_t *out, int heads, int rows, int row_start,
+                    int sequence_total, float v_bound, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(heads > 0 && rows > 0 && sequence_total > 0, "quant_v_fp8: empty problem");
+  H3S_CHECK_ARG(row_start >= 0 && row_start % 128 == 0, "quant_v_fp8: row_start %d must be 128 aligned", row_start);
+  H3S_CHECK_ARG(row_start + rows <= sequence_total, "quant_v_fp8: chunk exceeds sequence");
+  H3S_CHECK_ARG(rows % 128 == 0 || row_start + rows == sequence_total,
+                "quant_v_fp8: only the final chunk may contain a partial tile");
+  H3S_CHECK_ARG(v != nullptr && v_scale != nullptr && out != nullptr, "quant_v_fp8: NULL pointer");
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 15) == 0, "quant_v_fp8: out must be 16-byte aligned");
+  H3S_CHECK_ARG(v_bound > 0.f, "quant_v_fp8: v_bound must be positive");
+  { int rc = check_view(v, dtype, v_stride_h, v_stride_s, "quant_v_fp8 v"); if (rc) return rc; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case H3S_F32: return launch_quant_v<float>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
+    case H3S_BF16: return launch_quant_v<__nv_bfloat16>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
+    default: return launch_quant_v<__half>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
+  }
+}
+
+}  // extern "C"

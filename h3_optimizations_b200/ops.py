@@ -1,0 +1,248 @@
+"""Tensor-level wrappers over the C ABI (one function per entry point).
+
+All tensors must be CUDA tensors on the current device; every call launches on
+torch's current stream and returns without synchronising.  Shapes follow the
+reference's carriers: HND ``(1, H, S, 128)`` views with a contiguous last
+dimension, scales ``(1, H, blocks)``, V carrier ``(1, H, 128, pad128(S))``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _native
+from ._native import check, dtype_code, ptr, stream_ptr
+
+Q_TILE = 128
+KV_TILE = 64
+HEAD_DIM = 128
+FP8_V_BOUND = 448.0
+ATTN_P_SINGLE = 1
+
+
+def _ceil_div(a, b):
+    return (a + b - 1) // b
+
+
+def _hnd(x, what):
+    if x.ndim != 4 or x.shape[0] != 1 or x.shape[-1] != HEAD_DIM or x.stride(-1) != 1:
+        raise _native.NativeError("%s must be a (1,H,S,128) view with a contiguous last dimension" % what)
+    if not x.is_cuda:
+        raise _native.NativeError("%s must be a CUDA tensor (there is no CPU path)" % what)
+    return x.shape[1], x.shape[2]
+
+
+def device_capability():
+    code = _native.load().h3s_device_capability()
+    if code < 0:
+        check(code, "h3s_device_capability")
+    return code
+
+
+def column_stats(k=None, v=None, v_bound=FP8_V_BOUND):
+    """``(k_mean (1,H,128) | None, v_scale (1,H,128) | None)``."""
+    lib = _native.load()
+    ref = k if k is not None else v
+    heads, sequence = _hnd(ref, "column_stats input")
+    if k is not None and v is not None and (k.shape != v.shape or k.dtype != v.dtype):
+        raise _native.NativeError("column_stats: K and V must share shape and dtype")
+    scratch = torch.empty(lib.h3s_column_stats_scratch_bytes(heads), dtype=torch.uint8, device=ref.device)
+    k_mean = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=ref.device) if k is not None else None
+    v_scale = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=ref.device) if v is not None else None
+    check(
+        lib.h3s_column_stats(
+            ptr(k), k.stride(1) if k is not None else 0, k.stride(2) if k is not None else 0,
+            ptr(v), v.stride(1) if v is not None else 0, v.stride(2) if v is not None else 0,
+            dtype_code(ref.dtype), heads, sequence, float(v_bound), ptr(k_mean), ptr(v_scale), ptr(scratch),
+            stream_ptr(ref.device),
+        ),
+        "h3s_column_stats",
+    )
+    return k_mean, v_scale
+
+
+def quant_qk_blocks_into(x, out, scale, summary, *, block, row_start=0, mean=None):
+    """Quantise chunk ``x`` (1,H,rows,128) into rows ``[row_start, ...)`` of
+    ``out`` (1,H,S_total,128) int8; ``scale`` (1,H,blocks_total);
+    ``summary`` (1,H,blocks_total,128) or None.  ``out``/``scale`` may be None
+    (pooling only)."""
+    lib = _native.load()
+    heads, rows = _hnd(x, "quant_qk_blocks input")
+    if out is not None:
+        sequence_total = out.shape[2]
+        if out.dtype != torch.int8 or not out.is_contiguous() or out.shape[1] != heads:
+            raise _native.NativeError("quant_qk_blocks: carrier must be contiguous int8 (1,H,S,128)")
+        blocks_total = _ceil_div(sequence_total, block)
+        if scale is None or tuple(scale.shape) != (1, heads, blocks_total) or scale.dtype != torch.float32 or not scale.is_contiguous():
+            raise _native.NativeError("quant_qk_blocks: scale must be contiguous fp32 (1,H,%d)" % blocks_total)
+    else:
+        if summary is None:
+            raise _native.NativeError("quant_qk_blocks: nothing to produce")
+        sequence_total = None
+    if summary is not None:
+        blocks_total = summary.shape[2]
+        if sequence_total is None:
+            sequence_total = row_start + rows
+        if (tuple(summary.shape) != (1, heads, _ceil_div(sequence_total, block), HEAD_DIM)
+                or not summary.is_contiguous()):
+            raise _native.NativeError("quant_qk_blocks: summary must be contiguous (1,H,blocks,128)")
+    if mean is not None and (tuple(mean.shape) != (1, heads, HEAD_DIM) or mean.dtype != torch.float32 or not mean.is_contiguous()):
+        raise _native.NativeError("quant_qk_blocks: mean must be contiguous fp32 (1,H,128)")
+    check(
+        lib.h3s_quant_qk_blocks(
+            ptr(x), dtype_code(x.dtype), x.stride(1), x.stride(2), ptr(mean), ptr(out), ptr(scale),
+            ptr(summary), dtype_code(summary.dtype) if summary is not None else 0, heads, rows,
+            int(row_start), int(sequence_total), int(block), stream_ptr(x.device),
+        ),
+        "h3s_quant_qk_blocks",
+    )
+
+
+def quant_qk_blocks(x, block, *, mean=None, summary_dtype=None):
+    """``(codes int8 (1,H,S,128), scale (1,H,blocks), summary | None)``."""
+    heads, sequence = _hnd(x, "quant_qk_blocks input")
+    blocks = _ceil_div(sequence, block)
+    out = torch.empty((1, heads, sequence, HEAD_DIM), dtype=torch.int8, device=x.device)
+    scale = torch.empty((1, heads, blocks), dtype=torch.float32, device=x.device)
+    summary = None
+    if summary_dtype is not None:
+        summary = torch.empty((1, heads, blocks, HEAD_DIM), dtype=summary_dtype, device=x.device)
+    quant_qk_blocks_into(x, out, scale, summary, block=block, mean=mean)
+    return out, scale, summary
+
+
+def tile_means(x, block, dtype=torch.float64):
+    """Tile means only (no quantisation): ``(1,H,blocks,128)``."""
+    heads, sequence = _hnd(x, "tile_means input")
+    summary = torch.empty((1, heads, _ceil_div(sequence, block), HEAD_DIM), dtype=dtype, device=x.device)
+    quant_qk_blocks_into(x, None, None, summary, block=block)
+    return summary
+
+
+def allocate_v_carrier(sequence, heads, device):
+    """Zero-padded FP8 carrier ``(1,H,128,pad128(S))`` (reference:
+    attention/sparse/fp8_v_stream.py:69-75).  Not cleared: the quantiser
+    writes the padding itself."""
+    padded = _ceil_div(int(sequence), 128) * 128
+    return torch.empty((1, int(heads), HEAD_DIM, padded), dtype=torch.float8_e4m3fn, device=device)
+
+
+def quant_v_fp8_into(v, v_scale, carrier, *, row_start=0, sequence_total=None, v_bound=FP8_V_BOUND):
+    lib = _native.load()
+    heads, rows = _hnd(v, "quant_v_fp8 input")
+    sequence_total = int(sequence_total if sequence_total is not None else row_start + rows)
+    padded = _ceil_div(sequence_total, 128) * 128
+    if (tuple(carrier.shape) != (1, heads, HEAD_DIM, padded) or carrier.dtype != torch.float8_e4m3fn
+            or not carrier.is_contiguous()):
+        raise _native.NativeError("quant_v_fp8: carrier must be contiguous e4m3 (1,H,128,%d)" % padded)
+    if tuple(v_scale.shape) != (1, heads, HEAD_DIM) or v_scale.dtype != torch.float32 or not v_scale.is_contiguous():
+        raise _native.NativeError("quant_v_fp8: scale must be contiguous fp32 (1,H,128)")
+    check(
+        lib.h3s_quant_v_fp8(
+            ptr(v), dtype_code(v.dtype), v.stride(1), v.stride(2), ptr(v_scale), ptr(carrier), heads, rows,
+            int(row_start), sequence_total, float(v_bound), stream_ptr(v.device),
+        ),
+        "h3s_quant_v_fp8",
+    )
+
+
+def quant_v_fp8(v, v_scale=None, v_bound=FP8_V_BOUND):
+    """``(carrier e4m3 (1,H,128,pad128(S)), scale (1,H,128))``."""
+    heads, sequence = _hnd(v, "quant_v_fp8 input")
+    if v_scale is None:
+        _, v_scale = column_stats(None, v, v_bound)
+    carrier = allocate_v_carrier(sequence, heads, v.device)
+    quant_v_fp8_into(v, v_scale, carrier, v_bound=v_bound)
+    return carrier, v_scale
+
+
+def route_topk(q_summary, k_summary, *, q_start, q_stop, kv_start, kv_stop, retained):
+    """Compact route ``int32 (1,H,q_stop-q_start,route_len)``."""
+    lib = _native.load()
+    if q_summary.ndim != 4 or k_summary.ndim != 4 or q_summary.shape[0] != 1:
+        raise _native.NativeError("route_topk: summaries must be rank-4 (1,H,tiles,128)")
+    if q_summary.dtype != k_summary.dtype:
+        raise _native.NativeError("route_topk: summary dtypes differ")
+    q_summary = q_summary.contiguous()
+    k_summary = k_summary.contiguous()
+    heads, q_tiles = q_summary.shape[1], q_summary.shape[2]
+    kv_tiles = k_summary.shape[2]
+    route_len = kv_tiles - (kv_stop - kv_start) + retained
+    route = torch.empty((1, heads, q_stop - q_start, route_len), dtype=torch.int32, device=q_summary.device)
+    check(
+        lib.h3s_route_topk(
+            ptr(q_summary), ptr(k_summary), dtype_code(q_summary.dtype), heads, q_tiles, kv_tiles,
+            int(q_start), int(q_stop), int(kv_start), int(kv_stop), int(retained), ptr(route),
+            stream_ptr(q_summary.device),
+        ),
+        "h3s_route_topk",
+    )
+    return route
+
+
+def route_to_delta_lut(route, *, heads, q_tiles, kv_tiles, q_start, q_stop, device):
+    lib = _native.load()
+    lut = torch.empty((1, heads, q_tiles, kv_tiles), dtype=torch.int32, device=device)
+    valid = torch.empty((1, heads, q_tiles), dtype=torch.int32, device=device)
+    route_len = 0 if route is None else route.shape[-1]
+    check(
+        lib.h3s_route_to_delta_lut(
+            ptr(route), heads, q_tiles, kv_tiles, int(q_start), int(q_stop), int(route_len), ptr(lut),
+            ptr(valid), stream_ptr(device),
+        ),
+        "h3s_route_to_delta_lut",
+    )
+    return lut, valid
+
+
+def _attn_args(q8, k8, v_carrier, q_scale, k_scale, v_scale, route, q_start, q_stop, out):
+    heads, sequence = q8.shape[1], q8.shape[2]
+    for name, t, dt in (("q8", q8, torch.int8), ("k8", k8, torch.int8), ("v_carrier", v_carrier, torch.float8_e4m3fn),
+                        ("q_scale", q_scale, torch.float32), ("k_scale", k_scale, torch.float32),
+                        ("v_scale", v_scale, torch.float32)):
+        if t.dtype != dt or not t.is_contiguous() or not t.is_cuda:
+            raise _native.NativeError("sparse_attention: %s must be a contiguous CUDA %s tensor" % (name, dt))
+    padded = _ceil_div(sequence, 128) * 128
+    if tuple(k8.shape) != tuple(q8.shape) or tuple(v_carrier.shape) != (1, heads, HEAD_DIM, padded):
+        raise _native.NativeError("sparse_attention: carrier shapes do not agree")
+    if (tuple(q_scale.shape) != (1, heads, _ceil_div(sequence, Q_TILE))
+            or tuple(k_scale.shape) != (1, heads, _ceil_div(sequence, KV_TILE))
+            or tuple(v_scale.shape) != (1, heads, HEAD_DIM)):
+        raise _native.NativeError("sparse_attention: scale shapes do not agree")
+    route_len = 0
+    if route is not None:
+        if route.dtype != torch.int32 or not route.is_contiguous() or tuple(route.shape[:3]) != (1, heads, q_stop - q_start):
+            raise _native.NativeError("sparse_attention: route must be contiguous int32 (1,H,%d,len)" % (q_stop - q_start))
+        route_len = route.shape[-1]
+    if out.shape != q8.shape or out.stride(-1) != 1:
+        raise _native.NativeError("sparse_attention: output must be (1,H,S,128) with a contiguous last dimension")
+    return heads, sequence, route_len
+
+
+def new_attention_output(heads, sequence, dtype, device):
+    """HND view of a token-major ``(S, H*128)`` buffer, so the caller's
+    transpose+reshape before ``out_proj`` (attention_forward.py:123-128) is free."""
+    base = torch.empty((1, sequence, heads, HEAD_DIM), dtype=dtype, device=device)
+    return base.permute(0, 2, 1, 3)
+
+
+def sparse_attention(q8, k8, v_carrier, q_scale, k_scale, v_scale, route=None, *, q_start=0, q_stop=0,
+                     out=None, out_dtype=torch.bfloat16, status=None, legacy_mma=False, single_term_p=False):
+    """Launch the attention kernel.  Returns ``out`` (HND).  ``single_term_p``
+    carries the probabilities as one E4M3 term instead of hi + lo."""
+    lib = _native.load()
+    if out is None:
+        out = new_attention_output(q8.shape[1], q8.shape[2], out_dtype, q8.device)
+    heads, sequence, route_len = _attn_args(q8, k8, v_carrier, q_scale, k_scale, v_scale, route, q_start, q_stop, out)
+    common = (
+        ptr(q8), ptr(k8), ptr(v_carrier), ptr(q_scale), ptr(k_scale), ptr(v_scale), ptr(route), route_len,
+        int(q_start), int(q_stop), ptr(out), dtype_code(out.dtype), out.stride(1), out.stride(2), heads, sequence,
+    )
+    flags = ATTN_P_SINGLE if single_term_p else 0
+    if legacy_mma:
+        check(lib.h3s_sparse_attn_fwd_mma(*common, flags, stream_ptr(q8.device)), "h3s_sparse_attn_fwd_mma")
+    else:
+        check(lib.h3s_sparse_attn_fwd(*common, flags, ptr(status), stream_ptr(q8.device)), "h3s_sparse_attn_fwd")
+    return out

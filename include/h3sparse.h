@@ -1,0 +1,183 @@
+/*
+ * h3sparse.h - C ABI of the B200 (sm_100a) sparse-attention hot path.
+ *
+ * Every entry point takes raw device pointers, explicit strides/sizes and a
+ * CUDA stream, launches asynchronously on that stream, never allocates, never
+ * synchronises, and returns 0 on success or a negative H3S_E* code (message
+ * in h3s_last_error(), thread-local).  Strides are in ELEMENTS of the tensor
+ * they describe.  "HND" means a (heads, sequence, 128) view whose last
+ * dimension is contiguous; batch is always 1 (reference:
+ * attention/sparse/sparse_sage.py:448-449) - callers loop over batch.
+ *
+ * Each declaration cites the reference interface it replaces
+ * (file:line inside Pizzawookiee/H3-Optimizations).
+ */
+#ifndef H3SPARSE_H_
+#define H3SPARSE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define H3S_OK 0
+#define H3S_EINVAL (-1)   /* bad argument (shape, alignment, dtype)          */
+#define H3S_ECUDA (-2)    /* a CUDA runtime/driver call failed                */
+#define H3S_EARCH (-3)    /* device is not sm_100                             */
+#define H3S_ETIMEOUT (-4) /* a device-side bounded wait ran out (status word) */
+
+#define H3S_Q_TILE 128
+#define H3S_KV_TILE 64
+#define H3S_HEAD_DIM 128
+
+/* element types of floating inputs/outputs */
+#define H3S_F32 0
+#define H3S_BF16 1
+#define H3S_F16 2
+#define H3S_F64 3 /* router summaries only */
+
+typedef void *h3s_stream_t; /* cudaStream_t */
+
+/* Library / device ---------------------------------------------------- */
+
+/* ABI version of this header (bumped on any signature change). */
+int h3s_abi_version(void);
+/* Message of the last failing call on this host thread ("" if none). */
+const char *h3s_last_error(void);
+/* Compute capability of the current device as major*10+minor (100 on B200);
+ * replaces the capability gate of attention/sparse/sparse_sage.py:274-277. */
+int h3s_device_capability(void);
+
+/* Carrier quantisation -------------------------------------------------- */
+
+/* Bytes of scratch h3s_column_stats needs for `heads` heads. */
+size_t h3s_column_stats_scratch_bytes(int heads);
+
+/*
+ * Whole-sequence per-(head,channel) statistics, one pass over K and V:
+ *   k_mean[h,d] = mean_s K[h,s,d]  rounded to `dtype` and widened to fp32
+ *   v_scale[h,d] = max(max_s |V[h,s,d]| / v_bound, 1e-20)
+ * Either of k / v may be NULL (its output is then untouched).
+ * `scratch` (h3s_column_stats_scratch_bytes) is cleared by the call itself.
+ * Replaces `k.mean(dim=-2)` (attention/sparse/sparse_sage.py:319,
+ * sparse_quant.py:105) and update_v_amax / finalize_v_scale
+ * (attention/sparse/fp8_v_stream.py:58-66).
+ */
+int h3s_column_stats(const void *k, int64_t k_stride_h, int64_t k_stride_s,
+                     const void *v, int64_t v_stride_h, int64_t v_stride_s,
+                     int dtype, int heads, int sequence, float v_bound,
+                     float *k_mean, float *v_scale, void *scratch,
+                     h3s_stream_t stream);
+
+/*
+ * Per-block INT8 quantisation of an HND tensor (Q: block 128, K: block 64):
+ *   v = x - mean[h,:] (mean may be NULL);  scale = amax|v|/127 + 1e-7;
+ *   code = trunc(v/scale +- 0.5).
+ * Rows [0,rows) of `x` are rows [row_start,row_start+rows) of the carrier;
+ * row_start must be a multiple of `block`; only the last block may be ragged.
+ * out:      int8  (heads, sequence_total, 128) contiguous
+ * scale:    fp32  (heads, ceil(sequence_total/block))
+ * summary:  optional tile means, element type `summary_dtype`
+ *           (heads, blocks_total, 128); H3S_F64 stores the exact FP64 mean
+ *           used by the router, other types store the FP32 mean rounded.
+ * out and scale may both be NULL (pooling only: just the tile means).
+ * Replaces _quantize_blocks (attention/sparse/sparse_sage.py:312-330,
+ * sparse_quant.py:8-70) and pack_sparse_qk_chunk_into
+ * (attention/sparse/chunked_qkv.py:33-191).
+ */
+int h3s_quant_qk_blocks(const void *x, int dtype, int64_t x_stride_h,
+                        int64_t x_stride_s, const float *mean, int8_t *out,
+                        float *scale, void *summary, int summary_dtype,
+                        int heads, int rows, int row_start,
+                        int sequence_total, int block, h3s_stream_t stream);
+
+/*
+ * FP8-E4M3 V carrier: out[h,d,row_start+s] = e4m3(clamp(V[h,s,d]/scale[h,d],
+ * +-v_bound)); out is (heads, 128, pad128(sequence_total)) contiguous and the
+ * padding columns of the final chunk are written as zero.
+ * Replaces prepare_v / pack_v_chunk (attention/sparse/sparse_sage.py:84-110,
+ * attention/sparse/fp8_v_stream.py:14-55,78-140).
+ */
+int h3s_quant_v_fp8(const void *v, int dtype, int64_t v_stride_h,
+                    int64_t v_stride_s, const float *v_scale, uint8_t *out,
+                    int heads, int rows, int row_start, int sequence_total,
+                    float v_bound, h3s_stream_t stream);
+
+/* Router ---------------------------------------------------------------- */
+
+/*
+ * Top-`retained` pure-video KV tiles for every pure-video query tile, from
+ * tile means.  q_summary (heads,q_tiles,128), k_summary (heads,kv_tiles,128)
+ * of element type `dtype` (H3S_F64/F32/BF16/F16), contiguous.
+ * Pure-video tiles are [q_start,q_stop) and [kv_start,kv_stop).
+ * route: int32 (heads, q_stop-q_start, route_len) with
+ *   route_len = kv_tiles - (kv_stop-kv_start) + retained,
+ * each row = ascending absolute KV tile indices: the non-video tiles plus the
+ * selected ones.  Scores are exact FP64 dot products; equal scores keep the
+ * lower tile index.
+ * Replaces SparseTileRouter._build_lut_from_summaries / _pack_rows
+ * (attention/sparse/router.py:38-56,453-531) and
+ * build_compact_absolute_route (attention/sparse/triton_route.py:42-93).
+ */
+int h3s_route_topk(const void *q_summary, const void *k_summary, int dtype,
+                   int heads, int q_tiles, int kv_tiles, int q_start,
+                   int q_stop, int kv_start, int kv_stop, int retained,
+                   int32_t *route, h3s_stream_t stream);
+
+/*
+ * Expand a compact route into the reference's delta-encoded LUT
+ * lut int32 (heads,q_tiles,kv_tiles) and valid int32 (heads,q_tiles)
+ * (attention/sparse/router.py:219-240,453-475).  route may be NULL (dense).
+ */
+int h3s_route_to_delta_lut(const int32_t *route, int heads, int q_tiles,
+                           int kv_tiles, int q_start, int q_stop,
+                           int route_len, int32_t *lut, int32_t *valid,
+                           h3s_stream_t stream);
+
+/* Attention ------------------------------------------------------------- */
+
+#define H3S_ATTN_P_SINGLE 1
+
+/*
+ * Block-sparse attention on the carriers (tcgen05 kind::i8 QK^T into TMEM,
+ * FP32 online softmax, kind::f8f6f4 P.V, TMA loads of the listed KV tiles).
+ *   q8,k8   int8 (heads, sequence, 128) contiguous
+ *   v8t     e4m3 (heads, 128, pad128(sequence)) contiguous, zero padded
+ *   q_scale (heads, ceil(S/128)), k_scale (heads, ceil(S/64)), v_scale (heads,128)
+ *   route   int32 (heads, q_stop-q_start, route_len) or NULL for fully dense;
+ *           query tiles outside [q_start,q_stop) attend every KV tile.
+ *   out     element type out_dtype (BF16/F16/F32), strides in elements.
+ *   flags   0, or H3S_ATTN_P_SINGLE to carry P as one E4M3 term instead of
+ *           two (hi + lo): fewer MMAs, ~2.5e-2 instead of ~2e-3 relative error.
+ *   status  device int32[4]; word 0 is set non-zero if a bounded device wait
+ *           expired (the output is then invalid); may be NULL.
+ * Replaces the kernel call of attention/sparse/sparse_sage.py:112-121 and
+ * launch_int8_sparse (attention/sparse/triton_sparse_kernels.py:206-246).
+ */
+int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
+                        const float *q_scale, const float *k_scale,
+                        const float *v_scale, const int32_t *route,
+                        int route_len, int q_start, int q_stop, void *out,
+                        int out_dtype, int64_t out_stride_h,
+                        int64_t out_stride_s, int heads, int sequence,
+                        int flags, int32_t *status, h3s_stream_t stream);
+
+/*
+ * Same contract, legacy tensor path (mma.sync m16n8k32 s8 / e4m3).  Kept as
+ * the on-device cross-check of the tcgen05 kernel; not used by the backend.
+ */
+int h3s_sparse_attn_fwd_mma(const int8_t *q8, const int8_t *k8,
+                            const uint8_t *v8t, const float *q_scale,
+                            const float *k_scale, const float *v_scale,
+                            const int32_t *route, int route_len, int q_start,
+                            int q_stop, void *out, int out_dtype,
+                            int64_t out_stride_h, int64_t out_stride_s,
+                            int heads, int sequence, int flags,
+                            h3s_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* H3SPARSE_H_ */

@@ -1,0 +1,176 @@
+"""Attention kernels against the CPU oracle.  Needs a B200.
+
+Gate stated by the task: cosine >= 0.999 and relative max-abs <= 2e-2 against
+the INT8-QK / FP8-V reference math with FP32 probabilities.  The tighter
+implementation check compares with the oracle that rounds the probabilities
+exactly as the kernel does (two E4M3 terms)."""
+
+import pytest
+import torch
+
+from h3_optimizations_b200 import workloads
+from oracle import h3_oracle as oracle
+from tests.helpers import layout_of
+
+pytestmark = pytest.mark.gpu
+
+GATE_COS, GATE_REL = 0.999, 2e-2
+TIGHT_COS, TIGHT_REL = 0.99999, 4e-3
+
+
+@pytest.fixture(scope="module")
+def ops(native_lib):
+    from h3_optimizations_b200 import ops as module
+
+    return module
+
+
+def _carriers(q, k, v):
+    q8, qs = oracle.quantize_blocks(q, 128)
+    k8, ks = oracle.quantize_blocks(k, 64, subtract_mean=True)
+    vc, vs = oracle.v_fp8_carrier(v)
+    return q8, qs, k8, ks, vc, vs
+
+
+def _run(ops, carriers, route, geo, **kwargs):
+    q8, qs, k8, ks, vc, vs = (t.cuda() for t in carriers)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    out = ops.sparse_attention(
+        q8, k8, vc, qs, ks, vs, None if route is None else route.cuda().contiguous(),
+        q_start=geo.pure_video_q_start, q_stop=geo.pure_video_q_stop, status=status, **kwargs,
+    )
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0], "a bounded device wait expired: %s" % status.cpu().tolist()
+    return out
+
+
+CASES = [
+    # (sequence, video_start, heads, budget)
+    (129, 64, 1, 0.5),
+    (300, 44, 2, 0.5),
+    (350, 96, 2, 0.5),
+    (384, 128, 2, 1.0),   # dense
+    (640, 128, 3, 0.3),
+    (1000, 100, 2, 0.25),
+]
+
+
+@pytest.mark.parametrize("legacy", [False, True], ids=["tcgen05", "mma_sync"])
+@pytest.mark.parametrize("sequence,video_start,heads,budget", CASES)
+def test_small_cases_against_oracle(ops, sequence, video_start, heads, budget, legacy):
+    spec = workloads.small_spec("att", heads, video_start, sequence - video_start)
+    q, k, v = workloads.gaussian_qkv(spec, seed=sequence, widen=True)
+    geo, retained, selected, route = oracle.build_route(q, k, sequence, video_start, budget)
+    carriers = _carriers(q, k, v)
+    out = _run(ops, carriers, route, geo, out_dtype=torch.float32, legacy_mma=legacy).cpu()
+    tight = oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="e4m3x2")
+    m = oracle.compare(out, tight)
+    assert m["cosine"] >= TIGHT_COS and m["rel_max_abs"] <= TIGHT_REL, m
+    gate = oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="fp32")
+    m = oracle.compare(out, gate)
+    assert m["cosine"] >= GATE_COS and m["rel_max_abs"] <= GATE_REL, m
+
+
+def test_output_types_strides_and_determinism(ops):
+    spec = workloads.small_spec("att", 2, 128, 512)
+    q, k, v = workloads.gaussian_qkv(spec, seed=2, widen=True)
+    geo, retained, selected, route = oracle.build_route(q, k, 640, 128, 0.3)
+    carriers = _carriers(q, k, v)
+    ref = oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="e4m3x2")
+    first = _run(ops, carriers, route, geo, out_dtype=torch.float32)
+    again = _run(ops, carriers, route, geo, out_dtype=torch.float32)
+    assert torch.equal(first, again), "two launches on the same inputs must agree bit for bit"
+    for dtype, tol in ((torch.bfloat16, 1.2e-2), (torch.float16, 5e-3)):
+        out = _run(ops, carriers, route, geo, out_dtype=dtype)
+        assert out.dtype == dtype and tuple(out.shape) == (1, 2, 640, 128)
+        assert out.stride(2) == 2 * 128 and out.stride(1) == 128  # token-major buffer behind the HND view
+        assert oracle.compare(out.float().cpu(), ref)["rel_max_abs"] <= tol
+    contiguous = torch.empty((1, 2, 640, 128), dtype=torch.float32, device="cuda")
+    out = _run(ops, carriers, route, geo, out=contiguous)
+    assert torch.equal(out, first.contiguous())
+    single = _run(ops, carriers, route, geo, out_dtype=torch.float32, single_term_p=True).cpu()
+    m = oracle.compare(single, oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="e4m3"))
+    assert m["cosine"] >= TIGHT_COS and m["rel_max_abs"] <= TIGHT_REL, m
+
+
+def test_video_first_layout(ops):
+    spec = workloads.CONFIG0_VIDEO_FIRST
+    q, k, v = workloads.gaussian_qkv(spec, seed=0, widen=True)
+    geo, retained, selected, route = oracle.build_route(q, k, spec.sequence, 0, 0.3, video_stop=2048)
+    carriers = _carriers(q, k, v)
+    heads = [0, 3]
+    tiles = [0, 7, 15, 16, 17]
+    out = _run(ops, carriers, route, geo, out_dtype=torch.float32).cpu()
+    ref = oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="e4m3x2", heads=heads, q_tile_subset=tiles)
+    rows = torch.cat([torch.arange(t * 128, min(t * 128 + 128, spec.sequence)) for t in tiles])
+    m = oracle.compare(out[:, heads][:, :, rows], ref[:, heads][:, :, rows])
+    assert m["cosine"] >= TIGHT_COS and m["rel_max_abs"] <= TIGHT_REL, m
+
+
+def test_config0_through_the_backend(ops):
+    """BASELINE config 0 end to end through the plug-in surface: prepare()
+    (stats, quantisation, routing) + execute(), FP32 inputs."""
+    from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, runtime_options
+
+    spec = workloads.CONFIG0
+    q, k, v = workloads.gaussian_qkv(spec, seed=0, widen=True)
+    backend = B200SparseBackend(HybridSparseConfig(video_budget=0.3))
+    options = runtime_options(spec.layout(), step_index=5, total_steps=20)
+    prepared = backend.prepare(q.cuda(), k.cuda(), v.cuda(), layer_index=0, transformer_options=options)
+    out = backend.execute(prepared)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.float32 and tuple(out.shape) == (1, 4, 2304, 128)
+    geo, retained, selected, route = oracle.build_route(q, k, 2304, 256, 0.3)
+    assert torch.equal(prepared.sparse.route.indices.cpu(), route)
+    assert prepared.sparse.metadata["retained_video_kv_tiles"] == 10
+    carriers = _carriers(q, k, v)
+    gate = oracle.sparse_attention_int8_fp8(*carriers, geo, route, p_format="fp32")
+    m = oracle.compare(out.cpu(), gate)
+    assert m["cosine"] >= GATE_COS and m["rel_max_abs"] <= GATE_REL, m
+    flt = oracle.sparse_float_reference(q, k, v, geo, route)
+    report = oracle.compare(out.cpu(), flt)  # reported, not gated (INT8/FP8 carriers vs FP32 SDPA)
+    print("config0 vs FP32 SDPA on the same mask:", report)
+    assert report["cosine"] >= 0.999
+    lut, valid = backend.reference_lut(prepared)
+    olut, ovalid = oracle.delta_lut(selected, geo, 1, 4)
+    assert torch.equal(lut.cpu(), olut) and torch.equal(valid.cpu(), ovalid)
+
+
+def test_config1_full_size_sampled_against_oracle_and_cross_checked(ops):
+    """BASELINE config 1 (24 heads x 33272 tokens, 30 %): the whole layer runs
+    on the GPU; the CPU oracle checks a sample of (head, query tile) pairs -
+    dense, first/last routed and the ragged tail - and the mma.sync kernel
+    cross-checks every output row."""
+    from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, runtime_options
+
+    spec = workloads.CONFIG1
+    q, k, v = workloads.structured_qkv(spec, seed=0)
+    backend = B200SparseBackend(HybridSparseConfig(video_budget=0.3))
+    options = runtime_options(spec.layout())
+    prepared = backend.prepare(q.cuda(), k.cuda(), v.cuda(), layer_index=0, transformer_options=options)
+    sparse = prepared.sparse
+    out = backend.execute(prepared)
+    torch.cuda.synchronize()
+    assert sparse.route.route_len == 162 and sparse.metadata["full_mask_density"] == pytest.approx(0.32213, abs=1e-5)
+    geo = sparse.route.geometry
+    cross = ops.sparse_attention(
+        sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale, sparse.v_scale,
+        sparse.route.indices, q_start=geo.pure_video_q_start, q_stop=geo.pure_video_q_stop,
+        out_dtype=torch.bfloat16, legacy_mma=True,
+    )
+    torch.cuda.synchronize()
+    m = oracle.compare(out.float().cpu(), cross.float().cpu())
+    assert m["cosine"] >= 0.99999 and m["rel_max_abs"] <= 1e-2, m  # two bf16 roundings of the same math
+
+    ogeo = oracle.geometry(spec.sequence, 512)
+    route = sparse.route.indices.cpu()
+    tiles = [0, 3, 4, 130, 258, 259]
+    rows = torch.cat([torch.arange(t * 128, min(t * 128 + 128, spec.sequence)) for t in tiles])
+    for head in (0, 13, 23):
+        qh, kh, vh = (t[:, head:head + 1].float() for t in (q, k, v))
+        carriers = _carriers(qh, kh, vh)
+        gate = oracle.sparse_attention_int8_fp8(*carriers, ogeo, route[:, head:head + 1], p_format="fp32",
+                                                q_tile_subset=tiles)
+        got = out[:, head:head + 1].float().cpu()
+        m = oracle.compare(got[:, :, rows], gate[:, :, rows])
+        assert m["cosine"] >= GATE_COS and m["rel_max_abs"] <= GATE_REL, (head, m)
