@@ -1,0 +1,333 @@
+// Chunked ConvRot INT8 QKV projection for sm_100a.
+//
+//   convrot_quant_rows : x (rows, hidden) bf16 -> Hadamard-256 on every
+//                        256-channel group (fast Walsh-Hadamard in registers
+//                        and warp shuffles), per-row INT8 (scale = amax/127).
+//                        HBM-bound, one warp per 256-channel group.
+//   qkv_gemm_chunk     : persistent warp-specialised tcgen05 GEMM
+//                        acc[rows, n] = x_i8 . w_i8^T (kind::i8, int32 in TMEM),
+//                        128x256 tiles, K step 128 bytes (SWIZZLE_128B), 4-stage
+//                        TMA ring, two TMEM accumulators so the epilogue of one
+//                        tile overlaps the MMAs of the next.  The epilogue
+//                        de-quantises (acc * x_scale[row] * w_scale[col]), rounds
+//                        to bf16 and scatters into head-major (3*H, rows, 128)
+//                        staging that the carrier kernels consume.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tma.cuh"
+
+namespace h3s {
+
+// ---------------------------------------------------------------------------
+// ConvRot prologue
+// ---------------------------------------------------------------------------
+
+constexpr int kRotGroup = 256;
+
+// In-register part of the transform: butterflies over the three low index bits.
+__device__ __forceinline__ void fwht8(float (&v)[8]) {
+#pragma unroll
+  for (int stride = 1; stride < 8; stride <<= 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if ((i & stride) == 0) {
+        const float a = v[i], b = v[i + stride];
+        v[i] = __fadd_rn(a, b);
+        v[i + stride] = __fsub_rn(a, b);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(384)
+convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride, int rows, int hidden,
+                          int8_t *__restrict__ out, float *__restrict__ scale_out) {
+  extern __shared__ float warp_amax[];  // one per warp
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = hidden / kRotGroup;  // == warps per CTA
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    float v[8];
+    Elem<__nv_bfloat16>::load8(x + row * x_stride + warp * kRotGroup + lane * 8, v);
+    fwht8(v);
+#pragma unroll
+    for (int bit = 0; bit < 5; ++bit) {
+      const bool upper = (lane >> bit) & 1;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float other = __shfl_xor_sync(0xffffffffu, v[i], 1 << bit);
+        v[i] = upper ? __fsub_rn(other, v[i]) : __fadd_rn(v[i], other);
+      }
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[i] *= 0.0625f;  // 1/sqrt(256), exact
+      amax = fmaxf(amax, fabsf(v[i]));
+    }
+    amax = warp_max(amax);
+    __syncthreads();  // previous row's readers are done
+    if (lane == 0) warp_amax[warp] = amax;
+    __syncthreads();
+    amax = warp_amax[0];
+    for (int w = 1; w < groups; ++w) amax = fmaxf(amax, warp_amax[w]);
+    const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      int code = __float2int_rn(__fdiv_rn(v[i], scale));
+      code = max(-127, min(127, code));
+      packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+    }
+    *reinterpret_cast<uint2 *>(out + static_cast<int64_t>(row) * hidden + warp * kRotGroup + lane * 8) =
+        make_uint2(packed[0], packed[1]);
+    if (threadIdx.x == 0) scale_out[row] = scale;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// INT8 GEMM
+// ---------------------------------------------------------------------------
+
+constexpr int kGemmM = 128, kGemmN = 256, kGemmK = 128;  // K in bytes == int8 elements
+constexpr int kGemmStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kGemmABytes = kGemmM * kGemmK;  // 16384
+constexpr uint32_t kGemmBBytes = kGemmN * kGemmK;  // 32768
+constexpr uint32_t kGemmOffB = kGemmStages * kGemmABytes;
+constexpr uint32_t kGemmOffBar = kGemmOffB + kGemmStages * kGemmBBytes;
+constexpr uint32_t kGemmSmemBytes = kGemmOffBar + 256 + 1024;
+constexpr uint32_t kGemmTmemCols = 512;
+
+enum GemmAbort { kGemmAbortFull = 21, kGemmAbortEmpty, kGemmAbortAccFull, kGemmAbortAccEmpty };
+
+struct GemmShared {
+  uint64_t full[kGemmStages];
+  uint64_t empty[kGemmStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  int abort_word;
+};
+
+struct GemmParams {
+  const float *x_scale;   // (rows)
+  const float *w_scale;   // (n_out)
+  __nv_bfloat16 *out;     // (n_out/128, out_rows_stride/128.., 128): head-major staging
+  int64_t out_stride_head;  // elements between consecutive 128-column groups
+  int32_t *status;
+  int rows, n_out, hidden;
+  int m_tiles, n_tiles;
+};
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const GemmParams prm) {
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char *smem = reinterpret_cast<unsigned char *>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
+  GemmShared &sh = *reinterpret_cast<GemmShared *>(smem + kGemmOffBar);
+  volatile int *abort_word = &sh.abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int k_steps = prm.hidden / kGemmK;
+  const int total_tiles = prm.m_tiles * prm.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kGemmStages; ++i) {
+      ptx::mbar_init(&sh.full[i], 1);
+      ptx::mbar_init(&sh.empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&sh.acc_full[i], 1);
+      ptx::mbar_init(&sh.acc_empty[i], 4);
+    }
+    sh.abort_word = 0;
+    ptx::fence_mbar_init();
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(&sh.tmem_base, kGemmTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_a);
+      ptx::prefetch_tensormap(&map_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const int tm = tile % prm.m_tiles, tn = tile / prm.m_tiles;
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kGemmStages;
+          const uint32_t use = it / kGemmStages;
+          if (!ptx::mbar_wait(&sh.empty[s], (use & 1u) ^ 1u, abort_word, kGemmAbortEmpty)) { ok = false; break; }
+          ptx::mbar_arrive_expect_tx(&sh.full[s], kGemmABytes + kGemmBBytes);
+          ptx::tma_load_2d(smem + s * kGemmABytes, &map_a, &sh.full[s], ks * kGemmK, tm * kGemmM);
+          ptx::tma_load_2d(smem + kGemmOffB + s * kGemmBBytes, &map_b, &sh.full[s], ks * kGemmK, tn * kGemmN);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc(2, 1, 1, kGemmM, kGemmN);
+      uint32_t it = 0, local = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+        const int a = local & 1;
+        const uint32_t acc_use = local >> 1;
+        if (!ptx::mbar_wait(&sh.acc_empty[a], (acc_use & 1u) ^ 1u, abort_word, kGemmAbortAccEmpty)) { ok = false; break; }
+        ptx::tc_fence_after();
+        for (int ks = 0; ks < k_steps; ++ks, ++it) {
+          const int s = it % kGemmStages;
+          const uint32_t use = it / kGemmStages;
+          if (!ptx::mbar_wait(&sh.full[s], use & 1u, abort_word, kGemmAbortFull)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint64_t a_desc = ptx::umma_desc_kmajor(ptx::smem_u32(smem + s * kGemmABytes), 1024, ptx::kSwizzle128);
+          const uint64_t b_desc =
+              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kGemmOffB + s * kGemmBBytes), 1024, ptx::kSwizzle128);
+#pragma unroll
+          for (int k = 0; k < kGemmK / 32; ++k)
+            ptx::umma_i8(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          ptx::tc_commit(&sh.empty[s]);
+        }
+        if (ok) ptx::tc_commit(&sh.acc_full[a]);
+      }
+    }
+  } else {
+    // epilogue warps 0-3: thread <-> accumulator row
+    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    uint32_t local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
+      const int tm = tile % prm.m_tiles, tn = tile / prm.m_tiles;
+      const int a = local & 1;
+      const uint32_t acc_use = local >> 1;
+      {
+        const bool got = ptx::mbar_wait(&sh.acc_full[a], acc_use & 1u, abort_word, kGemmAbortAccFull);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      }
+      ptx::tc_fence_after();
+      const int row = tm * kGemmM + warp * 32 + lane;
+      const bool row_ok = row < prm.rows;
+      const float xs = row_ok ? __ldg(prm.x_scale + row) : 0.f;
+#pragma unroll 1
+      for (int cc = 0; cc < kGemmN / 32; ++cc) {
+        uint32_t acc[32];
+        H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + cc * 32, acc);
+        ptx::tmem_wait_ld();
+        const int col0 = tn * kGemmN + cc * 32;
+        if (row_ok && col0 < prm.n_out) {
+          const int group = col0 >> 7;  // 128-column group == (kind, head)
+          __nv_bfloat16 *dst = prm.out + group * prm.out_stride_head + static_cast<int64_t>(row) * H3S_HEAD_DIM + (col0 & 127);
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            uint32_t *wp = reinterpret_cast<uint32_t *>(&w);
+#pragma unroll
+            for (int e = 0; e < 8; e += 2) {
+              const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e])), xs), __ldg(prm.w_scale + col0 + i + e));
+              const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e + 1])), xs), __ldg(prm.w_scale + col0 + i + e + 1));
+              const __nv_bfloat162 t = __floats2bfloat162_rn(y0, y1);
+              wp[e >> 1] = *reinterpret_cast<const uint32_t *>(&t);
+            }
+            *reinterpret_cast<uint4 *>(dst + i) = w;
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&sh.acc_empty[a]);
+    }
+  }
+
+  __syncthreads();
+  const int code = sh.abort_word;
+  if (code != 0) {
+    __nanosleep(200000);
+    if (threadIdx.x == 0 && prm.status != nullptr) {
+      if (atomicCAS(prm.status, 0, code) == 0) prm.status[1] = blockIdx.x;
+    }
+  }
+  if (warp == 5) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem_base, kGemmTmemCols);
+  }
+}
+
+inline int make_tensor_map_u8_2d(CUtensorMap *map, const void *base, uint64_t dim0, uint64_t dim1,
+                                 uint64_t stride1_bytes, uint32_t box0, uint32_t box1, const char *what) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return fail(H3S_ECUDA, "%s: cuTensorMapEncodeTiled is unavailable", what);
+  const cuuint64_t dims[2] = {dim0, dim1};
+  const cuuint64_t strides[1] = {stride1_bytes};
+  const cuuint32_t box[2] = {box0, box1};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, elem,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return fail(H3S_ECUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, static_cast<int>(rc));
+  return H3S_OK;
+}
+
+}  // namespace h3s
+
+extern "C" {
+
+int h3s_convrot_quant_rows(const void *x, int64_t x_stride_row, int rows, int hidden, int8_t *x_i8,
+                           float *x_scale, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(x != nullptr && x_i8 != nullptr && x_scale != nullptr, "convrot_quant_rows: NULL pointer");
+  H3S_CHECK_ARG(rows > 0 && hidden > 0 && hidden % kRotGroup == 0 && hidden / kRotGroup <= 32,
+                "convrot_quant_rows: hidden %d must be a multiple of 256 and at most 8192", hidden);
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(x) & 15) == 0 && x_stride_row % 8 == 0 && x_stride_row >= hidden,
+                "convrot_quant_rows: input must be 16-byte aligned with a row stride that is a multiple of 8");
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(x_i8) & 7) == 0, "convrot_quant_rows: output must be 8-byte aligned");
+  const int groups = hidden / kRotGroup;
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  convrot_quant_rows_kernel<<<grid, groups * 32, groups * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16 *>(x), x_stride_row, rows, hidden, x_i8, x_scale);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8, const float *w_scale,
+                       int rows, int hidden, int n_out, void *out_bf16, int64_t out_stride_head,
+                       int32_t *status, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(x_i8 && x_scale && w_i8 && w_scale && out_bf16, "qkv_gemm_chunk: NULL pointer");
+  H3S_CHECK_ARG(rows > 0 && hidden > 0 && hidden % kGemmK == 0, "qkv_gemm_chunk: hidden %d must be a positive multiple of 128", hidden);
+  H3S_CHECK_ARG(n_out > 0 && n_out % H3S_HEAD_DIM == 0, "qkv_gemm_chunk: n_out %d must be a multiple of 128", n_out);
+  H3S_CHECK_ARG(out_stride_head >= static_cast<int64_t>(rows) * H3S_HEAD_DIM && out_stride_head % 8 == 0,
+                "qkv_gemm_chunk: out_stride_head %lld is smaller than rows*128", static_cast<long long>(out_stride_head));
+  H3S_CHECK_ARG(((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
+                "qkv_gemm_chunk: operands must be 16-byte aligned");
+  const int cap = h3s_device_capability();
+  if (cap < 0) return cap;
+  if (cap / 10 != 10) return fail(H3S_EARCH, "qkv_gemm_chunk: needs an sm_100 device, found sm_%d", cap);
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_u8_2d(&ma, x_i8, hidden, rows, hidden, kGemmK, kGemmM, "qkv_gemm_chunk A map");
+  if (rc) return rc;
+  rc = make_tensor_map_u8_2d(&mb, w_i8, hidden, n_out, hidden, kGemmK, kGemmN, "qkv_gemm_chunk B map");
+  if (rc) return rc;
+  GemmParams prm;
+  prm.x_scale = x_scale; prm.w_scale = w_scale; prm.out = static_cast<__nv_bfloat16 *>(out_bf16);
+  prm.out_stride_head = out_stride_head; prm.status = status;
+  prm.rows = rows; prm.n_out = n_out; prm.hidden = hidden;
+  prm.m_tiles = ceil_div(rows, kGemmM); prm.n_tiles = ceil_div(n_out, kGemmN);
+  int device = 0, sms = 0;
+  H3S_CHECK_CUDA(cudaGetDevice(&device));
+  H3S_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kGemmSmemBytes)));
+  const int tiles = prm.m_tiles * prm.n_tiles;
+  const int grid = tiles < sms ? tiles : sms;
+  qkv_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
+}
+
+}  // extern "C"
