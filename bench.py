@@ -56,6 +56,8 @@ def parse_args():
     parser.add_argument("--budget", type=float, default=VIDEO_BUDGET)
     parser.add_argument("--single-term-p", action="store_true",
                         help="carry P as one E4M3 term (faster, outside the parity gate on Gaussian V)")
+    parser.add_argument("--heads", type=int, default=0,
+                        help="run a head subset of the workload (profiling captures); 0 = all heads")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     return parser.parse_args()
@@ -194,6 +196,10 @@ def workload_name(spec, budget):
 def main():
     args = parse_args()
     spec = {"config1": workloads.CONFIG1, "config3": workloads.CONFIG3}[args.config]
+    if args.heads:
+        import dataclasses
+
+        spec = dataclasses.replace(spec, heads=args.heads, name="%s[%d heads]" % (spec.name, args.heads))
     if args.impl == "reference":
         run_reference(args, spec)
         return
