@@ -41,6 +41,8 @@ PROTOTYPES = {
     "h3s_column_stats_scratch_bytes": (c_size_t, [c_int]),
     "h3s_column_stats": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                                  c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "h3s_column_stats_static": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
+                                        c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "h3s_quant_qk_blocks": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "h3s_quant_v_fp8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_int, c_int,

@@ -19,7 +19,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 CSRC = PACKAGE_DIR / "csrc"
 LIB_DIR = PACKAGE_DIR / "_lib"
 LIB_PATH = LIB_DIR / "libh3sparse.so"
-SOURCES = ("api.cu", "quant.cu", "router.cu", "attn_tc.cu", "attn_mma.cu", "qkv_gemm.cu", "noalloc.cu")
+SOURCES = ("api.cu", "quant.cu", "router.cu", "attn_tc.cu", "attn_mma.cu", "qkv_gemm.cu")
 
 NVCC_FLAGS = (
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -4,6 +4,8 @@
 // Thread mapping shared by all three: 16 consecutive threads read one
 // 128-channel row as 16-byte vectors (8 channels each), so a warp covers two
 // full rows and every global load/store is a fully used 128/256/512-byte line.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace h3s {
@@ -336,6 +338,42 @@ static int launch_quant_v(const void *v, int64_t sh, int64_t ss, const float *v_
   return H3S_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch that lives inside the library image, for hosts that cannot hand
+// h3s_column_stats a scratch buffer of their own (see h3s_column_stats_static).
+// Every device that loads this library carries one copy (96 KiB) until the
+// process exits.  In host code the name below is only a stand-in for the
+// symbol; the device address comes from cudaGetSymbolAddress, once per device.
+// ---------------------------------------------------------------------------
+
+constexpr int kStaticStatsMaxHeads = 64;
+constexpr size_t kStaticStatsBytes =
+    static_cast<size_t>(kStaticStatsMaxHeads) * H3S_HEAD_DIM * (sizeof(double) + sizeof(unsigned int));
+static __device__ __align__(256) unsigned char g_static_stats_scratch[kStaticStatsBytes];
+
+constexpr int kStaticStatsMaxDevices = 64;
+static void *g_static_stats_addr[kStaticStatsMaxDevices] = {nullptr};
+static std::mutex g_static_stats_mutex;
+
+// Device address of the built-in scratch on the CURRENT device (looked up on
+// the first call for that device, cached afterwards).
+static int static_stats_scratch(void **out) {
+  int device = 0;
+  H3S_CHECK_CUDA(cudaGetDevice(&device));
+  H3S_CHECK_ARG(device >= 0 && device < kStaticStatsMaxDevices,
+                "column_stats_static: device ordinal %d is beyond the %d this library tracks", device,
+                kStaticStatsMaxDevices);
+  std::lock_guard<std::mutex> lock(g_static_stats_mutex);
+  if (g_static_stats_addr[device] == nullptr) {
+    void *ptr = nullptr;
+    H3S_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_static_stats_scratch));
+    H3S_CHECK_ARG(ptr != nullptr, "column_stats_static: the built-in scratch has no device address");
+    g_static_stats_addr[device] = ptr;
+  }
+  *out = g_static_stats_addr[device];
+  return H3S_OK;
+}
+
 }  // namespace h3s
 
 extern "C" {
@@ -409,6 +447,32 @@ int h3s_quant_v_fp8(const void *v, int dtype, int64_t v_stride_h, int64_t v_stri
     case H3S_F32: return launch_quant_v<float>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
     case H3S_BF16: return launch_quant_v<__nv_bfloat16>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
     default: return launch_quant_v<__half>(v, v_stride_h, v_stride_s, v_scale, out, heads, rows, row_start, sequence_total, v_bound, s);
+  }
+}
+
+
+int h3s_column_stats_static(const void *k, int64_t k_stride_h, int64_t k_stride_s, const void *v,
+                            int64_t v_stride_h, int64_t v_stride_s, int dtype, int heads, int sequence,
+                            float v_bound, float *k_mean, float *v_scale, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(heads > 0 && sequence > 0, "column_stats_static: empty problem (heads=%d sequence=%d)", heads, sequence);
+  H3S_CHECK_ARG(heads <= kStaticStatsMaxHeads,
+                "column_stats_static: %d heads exceed the %d the built-in scratch holds; use h3s_column_stats "
+                "with a caller-provided scratch buffer instead", heads, kStaticStatsMaxHeads);
+  H3S_CHECK_ARG(k != nullptr || v != nullptr, "column_stats_static: both inputs are NULL");
+  H3S_CHECK_ARG(k == nullptr || k_mean != nullptr, "column_stats_static: k given without k_mean");
+  H3S_CHECK_ARG(v == nullptr || (v_scale != nullptr && v_bound > 0.f), "column_stats_static: v given without v_scale/bound");
+  if (k != nullptr) { int rc = check_view(k, dtype, k_stride_h, k_stride_s, "column_stats_static k"); if (rc) return rc; }
+  if (v != nullptr) { int rc = check_view(v, dtype, v_stride_h, v_stride_s, "column_stats_static v"); if (rc) return rc; }
+  void *scratch = nullptr;
+  { int rc = static_stats_scratch(&scratch); if (rc) return rc; }
+  // launch_column_stats clears the part of the scratch it uses (a memset on the
+  // stream, not an allocation) before the accumulating kernel runs
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case H3S_F32: return launch_column_stats<float>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
+    case H3S_BF16: return launch_column_stats<__nv_bfloat16>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
+    default: return launch_column_stats<__half>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
   }
 }
 

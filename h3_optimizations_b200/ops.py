@@ -63,6 +63,32 @@ def column_stats(k=None, v=None, v_bound=FP8_V_BOUND):
     return k_mean, v_scale
 
 
+def column_stats_static_into(k, v, k_mean, v_scale, v_bound=FP8_V_BOUND):
+    """``column_stats`` into caller-owned ``k_mean`` / ``v_scale`` (fp32
+    ``(1,H,128)``) with the scratch that is built into the library, so nothing
+    is allocated by the call (at most 64 heads; calls that overlap on the GPU
+    race on the shared scratch)."""
+    lib = _native.load()
+    ref = k if k is not None else v
+    heads, sequence = _hnd(ref, "column_stats_static input")
+    if k is not None and v is not None and (k.shape != v.shape or k.dtype != v.dtype):
+        raise _native.NativeError("column_stats_static: K and V must share shape and dtype")
+    for name, t, src in (("k_mean", k_mean, k), ("v_scale", v_scale, v)):
+        if src is not None and (t is None or tuple(t.shape) != (1, heads, HEAD_DIM) or t.dtype != torch.float32
+                                or not t.is_contiguous() or t.device != ref.device):
+            raise _native.NativeError("column_stats_static: %s must be contiguous fp32 (1,H,128) on the input's device" % name)
+    check(
+        lib.h3s_column_stats_static(
+            ptr(k), k.stride(1) if k is not None else 0, k.stride(2) if k is not None else 0,
+            ptr(v), v.stride(1) if v is not None else 0, v.stride(2) if v is not None else 0,
+            dtype_code(ref.dtype), heads, sequence, float(v_bound), ptr(k_mean), ptr(v_scale),
+            stream_ptr(ref.device),
+        ),
+        "h3s_column_stats_static",
+    )
+    return k_mean, v_scale
+
+
 def quant_qk_blocks_into(x, out, scale, summary, *, block, row_start=0, mean=None):
     """Quantise chunk ``x`` (1,H,rows,128) into rows ``[row_start, ...)`` of
     ``out`` (1,H,S_total,128) int8; ``scale`` (1,H,blocks_total);

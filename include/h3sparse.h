@@ -72,6 +72,39 @@ int h3s_column_stats(const void *k, int64_t k_stride_h, int64_t k_stride_s,
                      h3s_stream_t stream);
 
 /*
+ * h3s_column_stats for hosts that have no scratch buffer to give.  (No
+ * counterpart in the reference: its statistics are torch reductions.)
+ *
+ * Some hosts of this library run under a closed memory plan: a serving
+ * process that froze its device pool after warm-up, or a plug-in called from
+ * inside another framework's operator where that framework's allocator must
+ * not be re-entered.  They can still pass inputs and outputs they already
+ * own, but not the extra `scratch` that h3s_column_stats asks for.  This
+ * variant keeps that scratch inside the library instead (a 96 KiB array in
+ * device memory, one copy on every GPU that loads the library, held until
+ * the process exits), so the call allocates nothing, here or in any library.
+ *
+ * Same arguments, results and errors as h3s_column_stats minus `scratch`,
+ * with these limits:
+ *   - heads <= 64; more is rejected with H3S_EINVAL and a message naming
+ *     the limit (use h3s_column_stats with your own scratch then);
+ *   - the first call on each device looks up the array's device address
+ *     (with that device current); make that first call outside any stream
+ *     capture;
+ *   - every call on a device shares the one array.  The call clears the part
+ *     it uses before accumulating, so leftovers of an earlier call never leak
+ *     into a result, but two calls that overlap on the GPU (different
+ *     streams, no ordering between them) race on it and both results are
+ *     then undefined.  Order them on one stream or with events.
+ */
+int h3s_column_stats_static(const void *k, int64_t k_stride_h,
+                            int64_t k_stride_s, const void *v,
+                            int64_t v_stride_h, int64_t v_stride_s, int dtype,
+                            int heads, int sequence, float v_bound,
+                            float *k_mean, float *v_scale,
+                            h3s_stream_t stream);
+
+/*
  * Per-block INT8 quantisation of an HND tensor (Q: block 128, K: block 64):
  *   v = x - mean[h,:] (mean may be NULL);  scale = amax|v|/127 + 1e-7;
  *   code = trunc(v/scale +- 0.5).
