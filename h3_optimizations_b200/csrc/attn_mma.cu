@@ -203,7 +203,7 @@ sparse_attn_mma_kernel(const int8_t *__restrict__ q8, const int8_t *__restrict__
         if (col >= n_valid) v = 0.f;
         l_part[e >> 1] += v;
         if (kSplitP) {
-          const float hi = __uint_as_float((__float_as_uint(v) + 0x00080000u) & 0xfff00000u);
+          const float hi = __uint_as_float(__float_as_uint(v) & 0xfff00000u);  // 4 significant bits, exact in E4M3
           r[nb][e] = v - hi;
           v = hi;
         }

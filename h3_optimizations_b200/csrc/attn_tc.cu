@@ -6,7 +6,7 @@
 //   P = exp2(c*S - m)  FP32 in registers, one thread per query row, m an integer
 //                      so every rescale is an exact power of two
 //   O += P8 . V8       tcgen05.mma kind::f8f6f4, 128x128x64, fp32 in TMEM
-// P is carried as two E4M3 terms (hi = P rounded to 4 significant bits,
+// P is carried as two E4M3 terms (hi = P truncated to 4 significant bits,
 // lo = E4M3(P - hi)) and the product is issued once per term, which gives the
 // probabilities ~7 significant bits; a single-term mode (flag
 // H3S_ATTN_P_SINGLE) trades that precision for fewer MMAs.
@@ -90,6 +90,30 @@ __device__ __forceinline__ float fast_exp2(float x) {
 __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word, int code) {
   const bool ok = ptx::mbar_wait(bar, parity, abort_word, code);
   return __all_sync(0xffffffffu, ok);
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
+// packed fp32x2 arithmetic (one instruction for two lanes of a 64-bit register pair)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(reinterpret_cast<unsigned long long &>(d))
+      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)),
+        "l"(reinterpret_cast<unsigned long long &>(c)));
+  return d;
+}
+
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("add.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long &>(d))
+      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
+  return d;
 }
 
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
@@ -284,16 +308,21 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const float c = q_scale * __ldg(k_scale + t);
       const int n_valid = min(H3S_KV_TILE, prm.sequence - t * H3S_KV_TILE);
 
-      int imax = INT_MIN;
-      if (n_valid == H3S_KV_TILE) {
+      // int32 scores -> fp32 in place; keys beyond the sequence (ragged last
+      // tile only) become -inf so they drop out of the maximum and give P = 0
+      float f[64];
 #pragma unroll
-        for (int i = 0; i < 64; ++i) imax = max(imax, static_cast<int>(s[i]));
-      } else {
+      for (int i = 0; i < 64; ++i) f[i] = static_cast<float>(static_cast<int>(s[i]));
+      if (n_valid < H3S_KV_TILE) {
 #pragma unroll
         for (int i = 0; i < 64; ++i)
-          if (i < n_valid) imax = max(imax, static_cast<int>(s[i]));
+          if (i >= n_valid) f[i] = -INFINITY;
       }
-      const float mx = c * static_cast<float>(imax);
+      float fm = max3(f[0], f[1], f[2]);
+#pragma unroll
+      for (int i = 3; i + 1 < 64; i += 2) fm = max3(fm, f[i], f[i + 1]);
+      fm = fmaxf(fm, f[63]);
+      const float mx = c * fm;  // c > 0
       const bool need = mx > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? ceilf(mx) - kPOffset : m_used;
@@ -319,28 +348,34 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         m_used = m_new;
       }
 
-      float sum = 0.f;
+      // P = exp2(c*f - m) two elements per instruction (packed fp32x2 FMA/ADD),
+      // hi = P truncated to 4 significant bits (exact in E4M3), lo = P - hi
+      const float2 c2 = make_float2(c, c), negm2 = make_float2(-m_used, -m_used), minus1 = make_float2(-1.f, -1.f);
+      float2 sum2 = make_float2(0.f, 0.f);
       uint32_t packed[16];
       uint32_t packed_lo[kSplitP ? 16 : 1];
 #pragma unroll
       for (int i = 0; i < 64; i += 4) {
-        float p[4], r[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          p[e] = fast_exp2(fmaf(c, static_cast<float>(static_cast<int>(s[i + e])), -m_used));
-          if (i + e >= n_valid) p[e] = 0.f;
-          sum += p[e];
-          if (kSplitP) {
-            // hi keeps 4 significant bits (exactly representable in E4M3), lo is the remainder
-            const float hi = __uint_as_float((__float_as_uint(p[e]) + 0x00080000u) & 0xfff00000u);
-            r[e] = p[e] - hi;
-            p[e] = hi;
-          }
+        float2 x01 = fma2(c2, make_float2(f[i], f[i + 1]), negm2);
+        float2 x23 = fma2(c2, make_float2(f[i + 2], f[i + 3]), negm2);
+        float2 p01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+        float2 p23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+        sum2 = add2(sum2, p01);
+        sum2 = add2(sum2, p23);
+        if (kSplitP) {
+          const float2 h01 = make_float2(__uint_as_float(__float_as_uint(p01.x) & 0xfff00000u),
+                                         __uint_as_float(__float_as_uint(p01.y) & 0xfff00000u));
+          const float2 h23 = make_float2(__uint_as_float(__float_as_uint(p23.x) & 0xfff00000u),
+                                         __uint_as_float(__float_as_uint(p23.y) & 0xfff00000u));
+          const float2 r01 = fma2(h01, minus1, p01);
+          const float2 r23 = fma2(h23, minus1, p23);
+          packed[i >> 2] = pack_e4m3x4(h01.x, h01.y, h23.x, h23.y);
+          packed_lo[i >> 2] = pack_e4m3x4(r01.x, r01.y, r23.x, r23.y);
+        } else {
+          packed[i >> 2] = pack_e4m3x4(p01.x, p01.y, p23.x, p23.y);
         }
-        packed[i >> 2] = pack_e4m3x4(p[0], p[1], p[2], p[3]);
-        if (kSplitP) packed_lo[i >> 2] = pack_e4m3x4(r[0], r[1], r[2], r[3]);
       }
-      l += sum;
+      l += sum2.x + sum2.y;
 
       if (!warp_wait(&sh.p_empty[b], (use & 1u) ^ 1u, abort_word, kAbortPEmpty)) { ok = false; break; }
       unsigned char *dst = p_row + 2 * b * kPBytes;

@@ -89,6 +89,31 @@ __global__ void column_stats_finalize_kernel(const double *__restrict__ k_sum,
   }
 }
 
+// Correctly rounded a/b for many a and one b: with r = RN(1/b),
+//   q0 = RN(a*r), e = a - b*q0 (exact in an FMA), q = RN(q0 + e*r)
+// equals RN(a/b) (Markstein) unless b's significand is all ones, where RN(1/b)
+// is not accurate enough; `exact` is false there and the IEEE divide is used.
+struct SharedDivisor {
+  float b, r;
+  bool exact;
+};
+
+__device__ __forceinline__ SharedDivisor make_divisor(float divisor) {
+  SharedDivisor d;
+  d.b = divisor;
+  d.r = __frcp_rn(divisor);
+  d.exact = (__float_as_uint(divisor) & 0x007fffffu) != 0x007fffffu && fabsf(divisor) > 1.0e-30f &&
+            fabsf(divisor) < 1.0e30f;
+  return d;
+}
+
+__device__ __forceinline__ float divide(const SharedDivisor &d, float a) {
+  if (!d.exact) return __fdiv_rn(a, d.b);
+  const float q0 = __fmul_rn(a, d.r);
+  const float e = __fmaf_rn(-d.b, q0, a);
+  return __fmaf_rn(e, d.r, q0);
+}
+
 // ---------------------------------------------------------------------------
 // Per-block INT8 quantisation with optional tile means.
 // One CTA = one (block, head); the whole block lives in registers
@@ -124,9 +149,9 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
   }
 
   float val[kPasses][8];
-  double col[8];
+  float col[8];  // this thread's rows (at most 8) summed in fp32, widened once
 #pragma unroll
-  for (int i = 0; i < 8; ++i) col[i] = 0.0;
+  for (int i = 0; i < 8; ++i) col[i] = 0.f;
   float amax = 0.f;
   const T *base = x + head * stride_h + c0;
 #pragma unroll
@@ -137,7 +162,7 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
       Elem<T>::load8(base + static_cast<int64_t>(first_row + r) * stride_s, raw);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        col[i] += static_cast<double>(raw[i]);
+        col[i] = __fadd_rn(col[i], raw[i]);
         val[p][i] = __fsub_rn(raw[i], mu[i]);
         amax = fmaxf(amax, fabsf(val[p][i]));
       }
@@ -150,13 +175,14 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
   if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x >> 5] = amax;
   if (summary != nullptr) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) red[slot][c0 + i] = col[i];
+    for (int i = 0; i < 8; ++i) red[slot][c0 + i] = static_cast<double>(col[i]);
   }
   __syncthreads();
   amax = warp_amax[0];
 #pragma unroll
   for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, warp_amax[w]);
   const float scale = __fadd_rn(__fdiv_rn(amax, 127.0f), 1.0e-7f);
+  const SharedDivisor by_scale = make_divisor(scale);
 
   const int global_block = row_start / BLOCK + local_block;
   if (threadIdx.x == 0 && scale_out != nullptr) scale_out[head * blocks_total + global_block] = scale;
@@ -170,7 +196,7 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
       uint32_t packed[2] = {0u, 0u};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float q = __fdiv_rn(val[p][i], scale);
+        float q = divide(by_scale, val[p][i]);
         q = __fadd_rn(q, q >= 0.f ? 0.5f : -0.5f);
         const int code = static_cast<int>(q);  // truncation toward zero
         packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
@@ -229,10 +255,15 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
   const int slot = threadIdx.x >> 4;
   const int c0 = (threadIdx.x & 15) * 8;
 
-  float sc[8];
+  float sc[8], rc[8];
+  bool all_exact = true;
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 8; ++i) {
     sc[i] = fmaxf(__ldg(v_scale + head * H3S_HEAD_DIM + c0 + i), 1.0e-20f);
+    const SharedDivisor d = make_divisor(sc[i]);
+    rc[i] = d.r;
+    all_exact = all_exact && d.exact;
+  }
 
   const T *base = v + head * stride_h + c0;
 #pragma unroll
@@ -248,7 +279,13 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
         Elem<T>::load8(base + static_cast<int64_t>(first_row + r0 + j) * stride_s, raw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float q = __fdiv_rn(raw[i], sc[i]);
+          float q;
+          if (all_exact) {  // shared-divisor division, see SharedDivisor
+            const float q0 = __fmul_rn(raw[i], rc[i]);
+            q = __fmaf_rn(__fmaf_rn(-sc[i], q0, raw[i]), rc[i], q0);
+          } else {
+            q = __fdiv_rn(raw[i], sc[i]);
+          }
           q = fminf(fmaxf(q, -v_bound), v_bound);
           const uint32_t code = __nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
           word[i] |= (code & 0xffu) << (8 * j);

@@ -184,6 +184,48 @@ def quant_v_fp8(v, v_scale=None, v_bound=FP8_V_BOUND):
     return carrier, v_scale
 
 
+def convrot_quant_rows(x, x_i8=None, x_scale=None):
+    """ConvRot (Hadamard-256) + per-row INT8 of ``x`` (rows, hidden) bf16.
+    Returns ``(codes int8 (rows, hidden), scale fp32 (rows,))``."""
+    lib = _native.load()
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_cuda or x.stride(1) != 1:
+        raise _native.NativeError("convrot_quant_rows: x must be a rank-2 CUDA bf16 tensor with contiguous rows")
+    rows, hidden = x.shape
+    if x_i8 is None:
+        x_i8 = torch.empty((rows, hidden), dtype=torch.int8, device=x.device)
+    if x_scale is None:
+        x_scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    if x_i8.shape[0] < rows or x_i8.shape[1] != hidden or not x_i8.is_contiguous() or x_scale.numel() < rows:
+        raise _native.NativeError("convrot_quant_rows: output buffers are too small")
+    check(
+        lib.h3s_convrot_quant_rows(ptr(x), x.stride(0), rows, hidden, ptr(x_i8), ptr(x_scale), stream_ptr(x.device)),
+        "h3s_convrot_quant_rows",
+    )
+    return x_i8[:rows], x_scale[:rows]
+
+
+def qkv_gemm_chunk(x_i8, x_scale, w_i8, w_scale, staging, *, row_start=0, status=None):
+    """INT8 GEMM of one chunk into ``staging`` bf16 ``(groups, S, 128)`` (group =
+    kind*H + head) at rows ``[row_start, row_start + rows)``."""
+    lib = _native.load()
+    rows, hidden = x_i8.shape
+    n_out = w_i8.shape[0]
+    if (x_i8.dtype != torch.int8 or w_i8.dtype != torch.int8 or not x_i8.is_contiguous() or not w_i8.is_contiguous()
+            or w_i8.shape[1] != hidden):
+        raise _native.NativeError("qkv_gemm_chunk: operands must be contiguous int8 with equal inner size")
+    if (staging.dtype != torch.bfloat16 or staging.ndim != 3 or staging.shape[0] * HEAD_DIM != n_out
+            or staging.shape[2] != HEAD_DIM or not staging.is_contiguous() or row_start + rows > staging.shape[1]):
+        raise _native.NativeError("qkv_gemm_chunk: staging must be contiguous bf16 (n_out/128, S, 128) with room for the chunk")
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 or x_scale.numel() < rows or w_scale.numel() != n_out:
+        raise _native.NativeError("qkv_gemm_chunk: scales must be fp32 (rows,) and (n_out,)")
+    base = ctypes.c_void_p(staging.data_ptr() + int(row_start) * HEAD_DIM * staging.element_size())
+    check(
+        lib.h3s_qkv_gemm_chunk(ptr(x_i8), ptr(x_scale), ptr(w_i8), ptr(w_scale), rows, hidden, n_out, base,
+                               staging.stride(0), ptr(status), stream_ptr(x_i8.device)),
+        "h3s_qkv_gemm_chunk",
+    )
+
+
 def route_topk(q_summary, k_summary, *, q_start, q_stop, kv_start, kv_stop, retained):
     """Compact route ``int32 (1,H,q_stop-q_start,route_len)``."""
     lib = _native.load()

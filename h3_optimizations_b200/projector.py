@@ -1,0 +1,150 @@
+"""Chunked native-carrier QKV provider for the B200 backend.
+
+Counterpart of the reference's ``ChunkedSparseQKVProjector``
+(attention/sparse/chunked_qkv.py:205-366): the packed ``x (S, hidden)`` is
+projected in 4096-row chunks straight into full-length quantised carriers, so
+no full-precision Q/K/V of the whole sequence is handed to the backend.
+
+Per chunk:  ConvRot (Hadamard-256) + per-row INT8 of the activations
+            -> tcgen05 INT8 GEMM against the INT8 QKV weight, de-quantised to
+               bf16 head-major staging
+            -> INT8 Q blocks (+ tile means) immediately.
+After the last chunk (K smoothing and the V scale need whole-sequence
+statistics): column statistics over the staged K and V, INT8 K blocks with the
+mean removed (+ tile means of the raw K), FP8-E4M3 V carrier.  With
+``smooth_k=False`` (what every chunked producer of the reference does,
+chunked_qkv.py:289) K is quantised per chunk as well.
+
+The module handed to ``project`` must expose ``heads``, ``head_dim`` and the
+INT8 weight in the rotated domain: ``qkv_weight_int8`` (3*H*128, hidden) with
+rows ordered ``[Q heads | K heads | V heads]`` (fused_qkv.py:195,394) and
+``qkv_weight_scale`` (3*H*128,) fp32.  Per-head RMSNorm and RoPE are not part
+of this provider yet: ``try_project`` declines (returns None) when
+``rope_freqs`` is given, which makes the forward boundary fall back to its own
+projection (attention_forward.py:78-96,161-177).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _native, ops
+from .carriers import PreparedFusedQKV, validate_prepared_fused_qkv
+from .errors import FusedQKVError
+from .router import KV_TILE, Q_TILE
+
+CHUNK_ROWS = 4096
+HEAD_DIM = 128
+V_QUANT_BOUND = 448.0
+
+
+def _validate_chunk_rows(chunk_rows, q_tile=Q_TILE, kv_tile=KV_TILE):
+    chunk_rows = int(chunk_rows)
+    alignment = math.lcm(int(q_tile), int(kv_tile))
+    if chunk_rows <= 0 or chunk_rows % alignment:
+        raise FusedQKVError(
+            "chunked Sparse Sage QKV rows must be a positive multiple of %d" % alignment
+        )
+    return chunk_rows
+
+
+def chunk_ranges(sequence, chunk_rows):
+    return [(start, min(start + chunk_rows, sequence)) for start in range(0, sequence, chunk_rows)]
+
+
+class ChunkedSparseQKVProjector:
+    name = "chunked_b200_sparse_qkv"
+    qk_format = "sparge_block_int8"
+
+    def __init__(self, chunk_rows=CHUNK_ROWS, *, smooth_k=True, summary_dtype=torch.float32):
+        self.chunk_rows = _validate_chunk_rows(chunk_rows)
+        self.smooth_k = bool(smooth_k)
+        self.summary_dtype = summary_dtype
+
+    @property
+    def installation_signature(self):
+        return (self.name, self.qk_format, self.chunk_rows, ("sm_100a", _native.ABI_VERSION, self.smooth_k))
+
+    # -- protocol ---------------------------------------------------------
+
+    def try_project(self, module, x, rope_freqs, *, layer_index, transformer_options):
+        if rope_freqs is not None:
+            return None
+        if getattr(module, "qkv_weight_int8", None) is None or getattr(module, "qkv_weight_scale", None) is None:
+            return None
+        return self.project(module, x, rope_freqs, layer_index=layer_index, transformer_options=transformer_options)
+
+    def project(self, module, x, rope_freqs, *, layer_index, transformer_options):
+        del transformer_options
+        if rope_freqs is not None:
+            raise FusedQKVError("the B200 chunked QKV provider does not apply RoPE; project without rope_freqs")
+        weight = getattr(module, "qkv_weight_int8", None)
+        scale = getattr(module, "qkv_weight_scale", None)
+        if weight is None or scale is None:
+            raise FusedQKVError("module does not expose qkv_weight_int8 / qkv_weight_scale")
+        return run_chunked_sparse_qkv(
+            x, weight, scale, heads=int(module.heads), head_dim=int(module.head_dim),
+            layer_index=layer_index, chunk_rows=self.chunk_rows, smooth_k=self.smooth_k,
+            summary_dtype=self.summary_dtype,
+        )
+
+
+def run_chunked_sparse_qkv(x, w_i8, w_scale, *, heads, head_dim=HEAD_DIM, layer_index=0,
+                           chunk_rows=CHUNK_ROWS, smooth_k=True, summary_dtype=torch.float32,
+                           status=None):
+    if not x.is_cuda or x.dtype != torch.bfloat16 or x.ndim != 2:
+        raise FusedQKVError("chunked Sparse Sage QKV requires a rank-2 CUDA BF16 input")
+    if torch.is_grad_enabled() and x.requires_grad:
+        raise FusedQKVError("chunked Sparse Sage QKV is inference-only")
+    if head_dim != HEAD_DIM:
+        raise FusedQKVError("chunked Sparse Sage QKV requires H3 head_dim 128")
+    chunk_rows = _validate_chunk_rows(chunk_rows)
+    sequence, hidden = int(x.shape[0]), int(x.shape[1])
+    n_out = 3 * heads * HEAD_DIM
+    if sequence <= 0 or tuple(w_i8.shape) != (n_out, hidden) or w_i8.dtype != torch.int8:
+        raise FusedQKVError("QKV weight must be int8 (3*heads*128, hidden) = (%d, %d)" % (n_out, hidden))
+    if tuple(w_scale.shape) != (n_out,) or w_scale.dtype != torch.float32:
+        raise FusedQKVError("QKV weight scale must be fp32 (%d,)" % n_out)
+    device = x.device
+    try:
+        q_blocks = (sequence + Q_TILE - 1) // Q_TILE
+        k_blocks = (sequence + KV_TILE - 1) // KV_TILE
+        shape = (1, heads, sequence, HEAD_DIM)
+        q_int8 = torch.empty(shape, dtype=torch.int8, device=device)
+        k_int8 = torch.empty(shape, dtype=torch.int8, device=device)
+        q_scale = torch.empty((1, heads, q_blocks), dtype=torch.float32, device=device)
+        k_scale = torch.empty((1, heads, k_blocks), dtype=torch.float32, device=device)
+        q_summary = torch.empty((1, heads, q_blocks, HEAD_DIM), dtype=summary_dtype, device=device)
+        k_summary = torch.empty((1, heads, k_blocks, HEAD_DIM), dtype=summary_dtype, device=device)
+        # head-major bf16 staging of the projection, whole sequence (K and V need
+        # whole-sequence statistics before they can be quantised)
+        staging = torch.empty((3 * heads, sequence, HEAD_DIM), dtype=torch.bfloat16, device=device)
+        x_i8 = torch.empty((min(chunk_rows, sequence), hidden), dtype=torch.int8, device=device)
+        x_scale = torch.empty((min(chunk_rows, sequence),), dtype=torch.float32, device=device)
+        q_stage = staging[:heads].unsqueeze(0)
+        k_stage = staging[heads:2 * heads].unsqueeze(0)
+        v_stage = staging[2 * heads:].unsqueeze(0)
+        w_i8 = w_i8.contiguous()
+        for start, end in chunk_ranges(sequence, chunk_rows):
+            rows = end - start
+            ops.convrot_quant_rows(x[start:end], x_i8, x_scale)
+            ops.qkv_gemm_chunk(x_i8[:rows], x_scale[:rows], w_i8, w_scale, staging, row_start=start, status=status)
+            ops.quant_qk_blocks_into(q_stage[:, :, start:end], q_int8, q_scale, q_summary, block=Q_TILE, row_start=start)
+            if not smooth_k:
+                ops.quant_qk_blocks_into(k_stage[:, :, start:end], k_int8, k_scale, k_summary, block=KV_TILE, row_start=start)
+        k_mean, v_scale = ops.column_stats(k_stage if smooth_k else None, v_stage, V_QUANT_BOUND)
+        if smooth_k:
+            ops.quant_qk_blocks_into(k_stage, k_int8, k_scale, k_summary, block=KV_TILE, mean=k_mean)
+        v_carrier, v_scale = ops.quant_v_fp8(v_stage, v_scale, V_QUANT_BOUND)
+    except _native.NativeError as exc:
+        raise FusedQKVError("chunked QKV projection failed: layer=%d: %s" % (layer_index, exc)) from exc
+    return validate_prepared_fused_qkv(
+        PreparedFusedQKV(
+            q_int8=q_int8, q_scale=q_scale, k_int8=k_int8, k_scale=k_scale, v=None,
+            q_summary=q_summary, k_summary=k_summary, output_dtype=x.dtype, sequence=sequence,
+            heads=heads, head_dim=HEAD_DIM, layer_index=int(layer_index), smooth_k=bool(smooth_k),
+            v_carrier=v_carrier, v_scale=v_scale,
+        )
+    )

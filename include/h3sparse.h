@@ -138,6 +138,45 @@ int h3s_quant_v_fp8(const void *v, int dtype, int64_t v_stride_h,
                     int heads, int rows, int row_start, int sequence_total,
                     float v_bound, h3s_stream_t stream);
 
+/* Chunked QKV projection -------------------------------------------------- */
+
+/*
+ * ConvRot activation quantisation for one chunk of rows: every 256-channel
+ * group of a row is rotated by the normalised Sylvester Hadamard matrix
+ * H256/16 (fast Walsh-Hadamard transform in FP32, stages in ascending stride
+ * order), then the row is quantised to INT8 with scale = amax/127 (1 when the
+ * row is zero), code = rint(v/scale) clamped to +-127.
+ *   x       bf16 (rows, hidden), row stride in elements, hidden % 256 == 0
+ *   x_i8    int8 (rows, hidden) contiguous;  x_scale fp32 (rows)
+ * Replaces comfy_kitchen quantize_int8_rowwise_convrot64(x, 256) as called at
+ * attention/sparse/fused_qkv.py:489-496 (the rotation itself is defined by the
+ * benchmark configuration; the reference does not vendor it).
+ */
+int h3s_convrot_quant_rows(const void *x, int64_t x_stride_row, int rows,
+                           int hidden, int8_t *x_i8, float *x_scale,
+                           h3s_stream_t stream);
+
+/*
+ * INT8 GEMM + de-quantisation for one chunk (tcgen05 kind::i8, TMA fed):
+ *   y[row, n] = bf16( float(sum_k x_i8[row,k] * w_i8[n,k]) * x_scale[row] * w_scale[n] )
+ * w_i8 int8 (n_out, hidden) contiguous, rows ordered [Q heads | K heads | V heads]
+ * (row kind*H*128 + head*128 + d); n_out and hidden multiples of 128.
+ * Output is head-major: 128-column group g (= kind*H + head) of row r lands at
+ *   out_bf16 + g*out_stride_head + r*128,
+ * so a (3*H, S, 128) staging tensor receives chunk rows [row_start, ...) when
+ * the caller offsets out_bf16 by row_start*128 and passes out_stride_head = S*128.
+ * status: optional device int32[4], word 0 non-zero if a bounded device wait
+ * expired.
+ * Replaces _fused_qk_kernel / _fused_v_kernel GEMM + dequant
+ * (attention/sparse/fused_qkv.py:198-223,370-438) and project_chunk_hnd
+ * (qkv/chunked.py:6-10).
+ */
+int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale,
+                       const int8_t *w_i8, const float *w_scale, int rows,
+                       int hidden, int n_out, void *out_bf16,
+                       int64_t out_stride_head, int32_t *status,
+                       h3s_stream_t stream);
+
 /* Router ---------------------------------------------------------------- */
 
 /*

@@ -362,7 +362,7 @@ def sparse_attention_int8_fp8(
     ``p_format='e4m3'`` rounds ``exp2(logit2 - ceil(rowmax) + 5)`` to FP8-E4M3
     before the product while the row sum stays FP32 - the arithmetic of the
     CUDA kernel's single-term mode.  ``p_format='e4m3x2'`` carries P as two
-    E4M3 terms, ``hi`` = P rounded to 4 significant bits and ``lo`` =
+    E4M3 terms, ``hi`` = P truncated to 4 significant bits and ``lo`` =
     E4M3(P - hi) - the kernel's default; used as the tight implementation
     check."""
     _, h_total, sequence, dim = q8.shape
@@ -395,7 +395,7 @@ def sparse_attention_int8_fp8(
             elif p_format == "e4m3x2":
                 p = torch.exp2(logits - (torch.ceil(row_max) - P_EXPONENT_OFFSET))
                 l = p.sum(dim=-1, keepdim=True)
-                hi = ((p.view(torch.int32) + 0x00080000) & -0x00100000).view(torch.float32)
+                hi = (p.view(torch.int32) & -0x00100000).view(torch.float32)
                 lo = (p - hi).to(torch.float8_e4m3fn).to(torch.float32)
                 p = hi.to(torch.float8_e4m3fn).to(torch.float32) + lo
             else:
@@ -454,14 +454,29 @@ def hadamard(n):
     return h
 
 
+def fwht_rows(x, group=256):
+    """Unnormalised fast Walsh-Hadamard transform of every ``group``-wide slice
+    of the last dimension, FP32, butterfly stages in ascending stride order
+    (1, 2, 4, ... group/2): the lower element of a pair becomes a+b, the upper
+    a-b.  Equals ``x @ hadamard(group)`` up to FP32 rounding; the CUDA prologue
+    uses the same stage order, so the two agree bit for bit."""
+    rows, channels = x.shape
+    v = x.float().reshape(rows, channels // group, group)
+    stride = 1
+    while stride < group:
+        w = v.reshape(rows, channels // group, group // (2 * stride), 2, stride)
+        a, b = w[..., 0, :], w[..., 1, :]
+        v = torch.stack((a + b, a - b), dim=-2).reshape(rows, channels // group, group)
+        stride *= 2
+    return v.reshape(rows, channels)
+
+
 def convrot_quantize_rows(x, group=256):
     """Rotate each ``group``-channel slice of every row by the normalised
-    Sylvester Hadamard ``H/sqrt(group)`` (FP32), then per-row INT8:
+    Sylvester Hadamard ``H/sqrt(group)`` (FP32 FWHT), then per-row INT8:
     ``scale = amax/127`` (1 when the row is zero), ``code = rint(v/scale)``
     clamped to +-127.  Returns ``(codes int8 (S,C), scale fp32 (S,))``."""
-    rows, channels = x.shape
-    rot = hadamard(group) / math.sqrt(group)
-    v = (x.float().reshape(rows, channels // group, group) @ rot).reshape(rows, channels)
+    v = fwht_rows(x, group) * (1.0 / math.sqrt(group))
     amax = v.abs().amax(dim=-1)
     scale = torch.where(amax > 0, amax / 127.0, torch.ones_like(amax))
     codes = torch.round(v / scale[:, None]).clamp_(-127, 127).to(torch.int8)
