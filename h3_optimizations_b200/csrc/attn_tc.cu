@@ -26,18 +26,16 @@
 
 namespace h3s {
 
-constexpr int kStages = 3;
+constexpr int kStages = 5;
 constexpr int kAttnThreads = 192;
 constexpr int kTmemCols = 256;
 constexpr uint32_t kQBytes = H3S_Q_TILE * H3S_HEAD_DIM;        // 16384
 constexpr uint32_t kKBytes = H3S_KV_TILE * H3S_HEAD_DIM;       // 8192
 constexpr uint32_t kVBytes = H3S_HEAD_DIM * H3S_KV_TILE;       // 8192
-constexpr uint32_t kPBytes = H3S_Q_TILE * H3S_KV_TILE;         // 8192
 constexpr uint32_t kOffQ = 0;
 constexpr uint32_t kOffK = kOffQ + kQBytes;
 constexpr uint32_t kOffV = kOffK + kStages * kKBytes;
-constexpr uint32_t kOffP = kOffV + kStages * kVBytes;
-constexpr uint32_t kOffBar = kOffP + 4 * kPBytes;  // P[buffer][hi|lo]
+constexpr uint32_t kOffBar = kOffV + kStages * kVBytes;  // P lives in TMEM, not in shared memory
 constexpr uint32_t kAttnSmemBytes = kOffBar + 1024 + 1024;  // barriers/scalars + alignment slack
 // P = exp2(logit - m) with m = ceil(rowmax) - kPOffset when m is (re)set, so the
 // largest probability starts in (16, 32]; m is raised again only when a tile
@@ -45,6 +43,7 @@ constexpr uint32_t kAttnSmemBytes = kOffBar + 1024 + 1024;  // barriers/scalars 
 // probabilities and the lo term above the E4M3 underflow threshold (2^-9).
 constexpr float kRescaleThreshold = 8.0f;
 constexpr float kPOffset = 5.0f;
+constexpr float kIntBias = 12582912.0f;  // 1.5 * 2^23: float(kIntBias + s) has bits 0x4b400000 + s
 
 enum AbortCode {
   kAbortQFull = 1, kAbortKvFull, kAbortKvEmpty, kAbortSFull, kAbortSEmpty, kAbortPFull, kAbortPEmpty,
@@ -105,6 +104,14 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
       : "=l"(reinterpret_cast<unsigned long long &>(d))
       : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)),
         "l"(reinterpret_cast<unsigned long long &>(c)));
+  return d;
+}
+
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<unsigned long long &>(d))
+      : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
   return d;
 }
 
@@ -262,14 +269,14 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           ptx::tc_fence_after();
           const uint64_t b_desc =
               ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV + s * kVBytes), 512, ptx::kSwizzle64);
+          // P(i) sits in TMEM on top of S buffer b: columns [0,16) hi, [16,32) lo,
+          // four E4M3 per column, 8 columns per K=32 step
 #pragma unroll
           for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
-            const uint64_t a_desc = ptx::umma_desc_kmajor(
-                ptx::smem_u32(smem + kOffP + (2 * b + term) * kPBytes), 512, ptx::kSwizzle64);
 #pragma unroll
             for (int k = 0; k < H3S_KV_TILE / 32; ++k)
-              ptx::umma_f8(tmem_o, a_desc + 2 * k, b_desc + 2 * k, idesc_pv,
-                           (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+              ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, b_desc + 2 * k, idesc_pv,
+                              (i > 0 || k > 0 || term > 0) ? 1u : 0u);
           }
           ptx::tc_commit(&sh.kv_empty[s]);
           ptx::tc_commit(&sh.p_empty[b]);
@@ -282,8 +289,6 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float q_scale = __ldg(prm.q_scale + head * prm.q_tiles + tq) * (0.08838834764831845f * 1.4426950408889634f);
     const float *k_scale = prm.k_scale + static_cast<int64_t>(head) * prm.kv_tiles;
-    unsigned char *p_row = smem + kOffP + row * H3S_KV_TILE;  // + (2*buffer + term) * kPBytes
-    const int swz = (row >> 1) & 3;
     float m_used = -INFINITY;
     float l = 0.f;
     bool ok = true;
@@ -308,20 +313,27 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const float c = q_scale * __ldg(k_scale + t);
       const int n_valid = min(H3S_KV_TILE, prm.sequence - t * H3S_KV_TILE);
 
-      // int32 scores -> fp32 in place; keys beyond the sequence (ragged last
-      // tile only) become -inf so they drop out of the maximum and give P = 0
+      // int32 scores -> fp32 without a conversion instruction: for |s| < 2^22,
+      // bits(12582912.0f) + s are the bits of the float 12582912 + s exactly, and
+      // the bias is folded into the FMA constant below.  Integer adds can issue
+      // on either the ALU or the FMA pipe.  Keys beyond the sequence (ragged
+      // last tile only) become -inf: out of the maximum, P = 0.
       float f[64];
 #pragma unroll
-      for (int i = 0; i < 64; ++i) f[i] = static_cast<float>(static_cast<int>(s[i]));
+      for (int i = 0; i < 64; ++i) f[i] = __uint_as_float(s[i] + 0x4b400000u);
       if (n_valid < H3S_KV_TILE) {
 #pragma unroll
         for (int i = 0; i < 64; ++i)
           if (i >= n_valid) f[i] = -INFINITY;
       }
+#ifdef H3S_PROBE_NOMAX  // timing probe only: wrong results after the first tile
+      float fm = j == 0 ? fmaxf(max3(f[0], f[1], f[2]), f[3]) + 40.f - kIntBias : -1.0e30f;
+#else
       float fm = max3(f[0], f[1], f[2]);
 #pragma unroll
       for (int i = 3; i + 1 < 64; i += 2) fm = max3(fm, f[i], f[i + 1]);
-      fm = fmaxf(fm, f[63]);
+      fm = fmaxf(fm, f[63]) - kIntBias;
+#endif
       const float mx = c * fm;  // c > 0
       const bool need = mx > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
@@ -350,7 +362,8 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
       // P = exp2(c*f - m) two elements per instruction (packed fp32x2 FMA/ADD),
       // hi = P truncated to 4 significant bits (exact in E4M3), lo = P - hi
-      const float2 c2 = make_float2(c, c), negm2 = make_float2(-m_used, -m_used), minus1 = make_float2(-1.f, -1.f);
+      const float bias = -fmaf(c, kIntBias, m_used);  // x = c*(f - 12582912) - m
+      const float2 c2 = make_float2(c, c), negm2 = make_float2(bias, bias), minus1 = make_float2(-1.f, -1.f);
       float2 sum2 = make_float2(0.f, 0.f);
       uint32_t packed[16];
       uint32_t packed_lo[kSplitP ? 16 : 1];
@@ -363,10 +376,18 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         sum2 = add2(sum2, p01);
         sum2 = add2(sum2, p23);
         if (kSplitP) {
+#ifdef H3S_PROBE_VELTKAMP
+          // hi = P rounded to 4 significant bits with FMA-pipe operations only
+          const float2 split = make_float2(1048577.f, 1048577.f);
+          const float2 g01 = mul2(p01, split), g23 = mul2(p23, split);
+          const float2 h01 = add2(g01, fma2(g01, minus1, p01));
+          const float2 h23 = add2(g23, fma2(g23, minus1, p23));
+#else
           const float2 h01 = make_float2(__uint_as_float(__float_as_uint(p01.x) & 0xfff00000u),
                                          __uint_as_float(__float_as_uint(p01.y) & 0xfff00000u));
           const float2 h23 = make_float2(__uint_as_float(__float_as_uint(p23.x) & 0xfff00000u),
                                          __uint_as_float(__float_as_uint(p23.y) & 0xfff00000u));
+#endif
           const float2 r01 = fma2(h01, minus1, p01);
           const float2 r23 = fma2(h23, minus1, p23);
           packed[i >> 2] = pack_e4m3x4(h01.x, h01.y, h23.x, h23.y);
@@ -377,17 +398,13 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       }
       l += sum2.x + sum2.y;
 
-      if (!warp_wait(&sh.p_empty[b], (use & 1u) ^ 1u, abort_word, kAbortPEmpty)) { ok = false; break; }
-      unsigned char *dst = p_row + 2 * b * kPBytes;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        *reinterpret_cast<uint4 *>(dst + ((ch ^ swz) << 4)) =
-            make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-        if (kSplitP)
-          *reinterpret_cast<uint4 *>(dst + kPBytes + ((ch ^ swz) << 4)) = make_uint4(
-              packed_lo[4 * ch], packed_lo[4 * ch + 1], packed_lo[4 * ch + 2], packed_lo[4 * ch + 3]);
-      }
-      ptx::fence_proxy_async_smem();
+      // P(j) overwrites this thread's own lane of S buffer b (already in
+      // registers).  The MMA that produced S(j) was issued after P.V(j-2), so
+      // nothing still reads these columns.
+      H3S_TMEM_ST16(tmem_s + lane_addr + b * H3S_KV_TILE, packed);
+      if (kSplitP) H3S_TMEM_ST16(tmem_s + lane_addr + b * H3S_KV_TILE + 16, packed_lo);
+      ptx::tmem_wait_st();
+      ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&sh.p_full[b]);
     }

@@ -37,20 +37,30 @@ struct Elem;
 template <>
 struct Elem<float> {
   static constexpr int kDtype = H3S_F32;
-  __device__ static void load8(const float *p, float (&v)[8]) {
-    const float4 a = __ldg(reinterpret_cast<const float4 *>(p));
-    const float4 b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-    v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  struct Raw { float4 a, b; };  // 8 elements as loaded
+  __device__ static Raw load_raw(const float *p) {
+    Raw r;
+    r.a = __ldg(reinterpret_cast<const float4 *>(p));
+    r.b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+    return r;
   }
+  __device__ static Raw zero_raw() { Raw r; r.a = make_float4(0.f, 0.f, 0.f, 0.f); r.b = r.a; return r; }
+  __device__ static void unpack(const Raw &r, float (&v)[8]) {
+    v[0] = r.a.x; v[1] = r.a.y; v[2] = r.a.z; v[3] = r.a.w;
+    v[4] = r.b.x; v[5] = r.b.y; v[6] = r.b.z; v[7] = r.b.w;
+  }
+  __device__ static void load8(const float *p, float (&v)[8]) { unpack(load_raw(p), v); }
   __device__ static float round_trip(float x) { return x; }
 };
 
 template <>
 struct Elem<__nv_bfloat16> {
   static constexpr int kDtype = H3S_BF16;
-  __device__ static void load8(const __nv_bfloat16 *p, float (&v)[8]) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
+  typedef uint4 Raw;  // 8 elements as loaded
+  __device__ static Raw load_raw(const __nv_bfloat16 *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+  __device__ static Raw zero_raw() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ static void load8(const __nv_bfloat16 *p, float (&v)[8]) { unpack(load_raw(p), v); }
+  __device__ static void unpack(const Raw &raw, float (&v)[8]) {
     const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -66,8 +76,11 @@ struct Elem<__nv_bfloat16> {
 template <>
 struct Elem<__half> {
   static constexpr int kDtype = H3S_F16;
-  __device__ static void load8(const __half *p, float (&v)[8]) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(p));
+  typedef uint4 Raw;  // 8 elements as loaded
+  __device__ static Raw load_raw(const __half *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
+  __device__ static Raw zero_raw() { return make_uint4(0u, 0u, 0u, 0u); }
+  __device__ static void load8(const __half *p, float (&v)[8]) { unpack(load_raw(p), v); }
+  __device__ static void unpack(const Raw &raw, float (&v)[8]) {
     const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {

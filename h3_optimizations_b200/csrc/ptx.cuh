@@ -15,6 +15,9 @@ namespace h3s {
 namespace ptx {
 
 constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s
+// A failed try_wait parks the thread in hardware for up to this long (it wakes
+// as soon as the phase completes), so waiting warps do not burn issue slots.
+constexpr uint32_t kSuspendHintNs = 20000u;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -50,11 +53,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t"
       "}\n"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }
@@ -69,7 +72,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 15u) == 0u) {
       if (*abort_word != 0) return false;
       if (global_timer_ns() - start > kWaitBudgetNs) {
         atomicCAS(const_cast<int *>(abort_word), 0, code);
@@ -198,6 +201,20 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// A operand taken from TMEM (rows = lanes, 8-bit elements packed four per
+// 32-bit column), B from shared memory.
+__device__ __forceinline__ void umma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // ---- tcgen05: TMEM <-> registers (whole warp; lane i <-> TMEM lane base+i) ----
 
 #define H3S_TMEM_LD32(taddr, r)                                                                      \
@@ -223,6 +240,15 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
         "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),          \
         "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),          \
         "r"(r[29]), "r"(r[30]), "r"(r[31])                                                           \
+      : "memory")
+
+#define H3S_TMEM_ST16(taddr, r)                                                                      \
+  asm volatile(                                                                                      \
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "                                                \
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"                                    \
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),     \
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), \
+        "r"(r[15])                                                                                   \
       : "memory")
 
 __device__ __forceinline__ void tmem_wait_ld() {

@@ -116,12 +116,13 @@ __device__ __forceinline__ float divide(const SharedDivisor &d, float a) {
 
 // ---------------------------------------------------------------------------
 // Per-block INT8 quantisation with optional tile means.
-// One CTA = one (block, head); the whole block lives in registers
-// (64 values per thread) between the amax reduction and the store.
+// One CTA = one (block, head); the whole block lives in registers, as loaded
+// (64 values per thread, 32 registers for 16-bit inputs), between the amax
+// reduction and the store, so it is read from memory exactly once.
 // ---------------------------------------------------------------------------
 
 template <typename T, int BLOCK>
-__global__ void __launch_bounds__(BLOCK * 2)
+__global__ void __launch_bounds__(BLOCK * 2, (sizeof(T) == 2 ? 1024 : 512) / (BLOCK * 2))
 quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride_s,
                        const float *__restrict__ mean, int8_t *__restrict__ out,
                        float *__restrict__ scale_out, void *__restrict__ summary,
@@ -148,7 +149,7 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
     for (int i = 0; i < 8; ++i) mu[i] = __ldg(mean + head * H3S_HEAD_DIM + c0 + i);
   }
 
-  float val[kPasses][8];
+  typename Elem<T>::Raw raw[kPasses];
   float col[8];  // this thread's rows (at most 8) summed in fp32, widened once
 #pragma unroll
   for (int i = 0; i < 8; ++i) col[i] = 0.f;
@@ -157,18 +158,20 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
 #pragma unroll
   for (int p = 0; p < kPasses; ++p) {
     const int r = p * kSlots + slot;
+    raw[p] = r < valid_rows ? Elem<T>::load_raw(base + static_cast<int64_t>(first_row + r) * stride_s)
+                            : Elem<T>::zero_raw();
+  }
+#pragma unroll
+  for (int p = 0; p < kPasses; ++p) {
+    const int r = p * kSlots + slot;
     if (r < valid_rows) {
-      float raw[8];
-      Elem<T>::load8(base + static_cast<int64_t>(first_row + r) * stride_s, raw);
+      float v[8];
+      Elem<T>::unpack(raw[p], v);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        col[i] = __fadd_rn(col[i], raw[i]);
-        val[p][i] = __fsub_rn(raw[i], mu[i]);
-        amax = fmaxf(amax, fabsf(val[p][i]));
+        col[i] = __fadd_rn(col[i], v[i]);
+        amax = fmaxf(amax, fabsf(__fsub_rn(v[i], mu[i])));
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) val[p][i] = 0.f;
     }
   }
   amax = warp_max(amax);
@@ -193,10 +196,12 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
   for (int p = 0; p < kPasses; ++p) {
     const int r = p * kSlots + slot;
     if (out != nullptr && r < valid_rows) {
+      float v[8];
+      Elem<T>::unpack(raw[p], v);
       uint32_t packed[2] = {0u, 0u};
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float q = divide(by_scale, val[p][i]);
+        float q = divide(by_scale, __fsub_rn(v[i], mu[i]));
         q = __fadd_rn(q, q >= 0.f ? 0.5f : -0.5f);
         const int code = static_cast<int>(q);  // truncation toward zero
         packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);

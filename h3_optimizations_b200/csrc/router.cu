@@ -1,19 +1,18 @@
 // Block router: exact FP64 tile-mean scores, per-row radix top-k, ordered
 // emission of the packed KV-tile index list.
 //
-// One CTA scores kRows pure-video query tiles of one head against every
-// pure-video KV tile (scores kept in shared memory), then each warp owns one
-// row: an 8-pass MSB-first radix select on order-preserving 64-bit keys finds
-// the retained-th largest score exactly, and a ballot-ordered sweep writes
-// the surviving tile indices in ascending order, so no sort is needed.
+// One CTA scores 8 pure-video query tiles of one head against every
+// pure-video KV tile with FP64 tensor-core MMAs (scores kept in shared
+// memory), then each warp owns one row: an 8-pass MSB-first radix select on
+// order-preserving 64-bit keys finds the retained-th largest score exactly,
+// and a ballot-ordered sweep writes the surviving tile indices in ascending
+// order, so no sort is needed.
 #include "common.cuh"
 
 namespace h3s {
 
 constexpr int kRouteRows = 8;         // query tiles per CTA == warps per CTA
 constexpr int kRouteThreads = kRouteRows * 32;
-constexpr int kRouteKChunk = 32;      // KV tiles staged per step
-constexpr int kRoutePitch = H3S_HEAD_DIM + 1;  // doubles; keeps 64-bit loads conflict-free
 
 template <typename T> __device__ __forceinline__ double to_double(T v);
 template <> __device__ __forceinline__ double to_double<double>(double v) { return v; }
@@ -35,9 +34,7 @@ route_topk_kernel(const T *__restrict__ q_summary, const T *__restrict__ k_summa
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int pure_q = q_stop - q_start;
   const int pure_kv = kv_stop - kv_start;
-  double *q_rows = reinterpret_cast<double *>(smem_raw);                    // [kRouteRows][128]
-  double *k_stage = q_rows + kRouteRows * H3S_HEAD_DIM;                     // [kRouteKChunk][pitch]
-  double *scores = k_stage + kRouteKChunk * kRoutePitch;                    // [kRouteRows][pure_kv]
+  double *scores = reinterpret_cast<double *>(smem_raw);                                     // [kRouteRows][pure_kv]
   int *hist = reinterpret_cast<int *>(scores + static_cast<size_t>(kRouteRows) * pure_kv);  // [rows][256]
 
   const int head = blockIdx.y;
@@ -45,30 +42,33 @@ route_topk_kernel(const T *__restrict__ q_summary, const T *__restrict__ k_summa
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  for (int i = threadIdx.x; i < kRouteRows * H3S_HEAD_DIM; i += kRouteThreads) {
-    const int r = i / H3S_HEAD_DIM, d = i % H3S_HEAD_DIM;
-    const int row = min(row0 + r, pure_q - 1);
-    q_rows[i] = to_double(q_summary[(static_cast<int64_t>(head) * q_tiles + q_start + row) * H3S_HEAD_DIM + d]);
-  }
-
-  // ---- scores[r][p] = <q_rows[r], k[p]> in FP64 ----
-  for (int p0 = 0; p0 < pure_kv; p0 += kRouteKChunk) {
-    __syncthreads();
-    for (int i = threadIdx.x; i < kRouteKChunk * H3S_HEAD_DIM; i += kRouteThreads) {
-      const int kk = i / H3S_HEAD_DIM, d = i % H3S_HEAD_DIM;
-      const int p = min(p0 + kk, pure_kv - 1);
-      k_stage[kk * kRoutePitch + d] =
-          to_double(k_summary[(static_cast<int64_t>(head) * kv_tiles + kv_start + p) * H3S_HEAD_DIM + d]);
-    }
-    __syncthreads();
-    const int kk = lane, r = warp;
-    if (p0 + kk < pure_kv) {
-      const double *qv = q_rows + r * H3S_HEAD_DIM;
-      const double *kv = k_stage + kk * kRoutePitch;
-      double acc = 0.0;
-#pragma unroll 16
-      for (int d = 0; d < H3S_HEAD_DIM; ++d) acc = fma(qv[d], kv[d], acc);
-      scores[static_cast<size_t>(r) * pure_kv + p0 + kk] = acc;
+  // ---- scores[r][p] = <q[r], k[p]> in FP64 on the tensor cores ----
+  // mma.m8n8k4.f64: A is the CTA's 8 query tiles x 4 channels, B 4 channels x 8
+  // KV tiles; lane l holds A[l/4][l%4], B[l%4][l/4] and C[l/4][2*(l%4) + {0,1}].
+  // The 32 A fragments of a lane (all 128 channels) stay in registers; every
+  // warp walks its own KV blocks and reads the K means straight from L2.
+  {
+    const int frag_row = lane >> 2, frag_k = lane & 3;
+    const int a_row = min(row0 + frag_row, pure_q - 1);
+    const T *qp = q_summary + (static_cast<int64_t>(head) * q_tiles + q_start + a_row) * H3S_HEAD_DIM + frag_k;
+    double a[H3S_HEAD_DIM / 4];
+#pragma unroll
+    for (int kk = 0; kk < H3S_HEAD_DIM / 4; ++kk) a[kk] = to_double(qp[4 * kk]);
+    const int n_blocks = (pure_kv + 7) >> 3;
+    for (int nb = warp; nb < n_blocks; nb += kRouteRows) {
+      const int b_row = min(8 * nb + frag_row, pure_kv - 1);
+      const T *kp = k_summary + (static_cast<int64_t>(head) * kv_tiles + kv_start + b_row) * H3S_HEAD_DIM + frag_k;
+      double c0 = 0.0, c1 = 0.0;
+#pragma unroll
+      for (int kk = 0; kk < H3S_HEAD_DIM / 4; ++kk) {
+        const double b = to_double(kp[4 * kk]);
+        asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
+                     : "+d"(c0), "+d"(c1)
+                     : "d"(a[kk]), "d"(b));
+      }
+      const int col = 8 * nb + 2 * frag_k;
+      if (col < pure_kv) scores[static_cast<size_t>(frag_row) * pure_kv + col] = c0;
+      if (col + 1 < pure_kv) scores[static_cast<size_t>(frag_row) * pure_kv + col + 1] = c1;
     }
   }
   __syncthreads();
@@ -165,9 +165,7 @@ static int launch_route(const void *q_summary, const void *k_summary, int heads,
                         int q_start, int q_stop, int kv_start, int kv_stop, int retained, int route_len,
                         int32_t *route, cudaStream_t stream) {
   const int pure_q = q_stop - q_start, pure_kv = kv_stop - kv_start;
-  const size_t smem = sizeof(double) * (kRouteRows * H3S_HEAD_DIM + kRouteKChunk * kRoutePitch +
-                                        static_cast<size_t>(kRouteRows) * pure_kv) +
-                      sizeof(int) * kRouteRows * 256;
+  const size_t smem = sizeof(double) * static_cast<size_t>(kRouteRows) * pure_kv + sizeof(int) * kRouteRows * 256;
   H3S_CHECK_ARG(smem <= 220 * 1024, "route_topk: %d pure-video KV tiles need %zu bytes of shared memory", pure_kv, smem);
   H3S_CHECK_CUDA(cudaFuncSetAttribute(route_topk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   dim3 grid(ceil_div(pure_q, kRouteRows), heads);
