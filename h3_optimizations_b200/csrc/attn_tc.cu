@@ -73,6 +73,8 @@ struct AttnShared {
   uint64_t p_empty[2];
   uint32_t tmem_base;
   int abort_word;
+  int tile_index[kStages];    // KV tile held by each stage ...
+  float tile_scale[kStages];  // ... and its k_scale, written by the producer
   float v_scale[H3S_HEAD_DIM];
 };
 static_assert(sizeof(AttnShared) <= 1024, "barrier block too large");
@@ -223,20 +225,42 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
   if (warp == 4) {
     // =================== TMA producer ===================
+    // The whole warp fetches the tile indices and K scales of 32 tiles at a
+    // time (two dependent global loads, kept off everybody's critical path);
+    // lane 0 then feeds the stage ring and leaves each stage's index and scale
+    // in shared memory for the softmax warps.
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_q);
       ptx::prefetch_tensormap(&map_k);
       ptx::prefetch_tensormap(&map_v);
       ptx::mbar_arrive_expect_tx(&sh.q_full, kQBytes);
       ptx::tma_load_3d(smem + kOffQ, &map_q, &sh.q_full, 0, tq * H3S_Q_TILE, head);
-      for (int j = 0; j < n_iter; ++j) {
-        const int s = j % kStages;
-        const uint32_t use = static_cast<uint32_t>(j / kStages);
-        if (!ptx::mbar_wait(&sh.kv_empty[s], (use & 1u) ^ 1u, abort_word, kAbortKvEmpty)) break;
-        const int t = dense ? j : __ldg(route_row + j);
-        ptx::mbar_arrive_expect_tx(&sh.kv_full[s], kKBytes + kVBytes);
-        ptx::tma_load_3d(smem + kOffK + s * kKBytes, &map_k, &sh.kv_full[s], 0, t * H3S_KV_TILE, head);
-        ptx::tma_load_3d(smem + kOffV + s * kVBytes, &map_v, &sh.kv_full[s], t * H3S_KV_TILE, 0, head);
+    }
+    const float *k_scale = prm.k_scale + static_cast<int64_t>(head) * prm.kv_tiles;
+    bool ok = true;
+    for (int j0 = 0; ok && j0 < n_iter; j0 += 32) {
+      const int mine = min(j0 + lane, n_iter - 1);
+      const int my_tile = dense ? mine : __ldg(route_row + mine);
+      const float my_scale = __ldg(k_scale + my_tile);
+      const int batch = min(32, n_iter - j0);
+      for (int i = 0; i < batch; ++i) {
+        const int t = __shfl_sync(0xffffffffu, my_tile, i);
+        const float ks = __shfl_sync(0xffffffffu, my_scale, i);
+        if (lane == 0) {
+          const int j = j0 + i;
+          const int s = j % kStages;
+          const uint32_t use = static_cast<uint32_t>(j / kStages);
+          ok = ptx::mbar_wait(&sh.kv_empty[s], (use & 1u) ^ 1u, abort_word, kAbortKvEmpty);
+          if (ok) {
+            sh.tile_index[s] = t;
+            sh.tile_scale[s] = ks;
+            ptx::mbar_arrive_expect_tx(&sh.kv_full[s], kKBytes + kVBytes);
+            ptx::tma_load_3d(smem + kOffK + s * kKBytes, &map_k, &sh.kv_full[s], 0, t * H3S_KV_TILE, head);
+            ptx::tma_load_3d(smem + kOffV + s * kVBytes, &map_v, &sh.kv_full[s], t * H3S_KV_TILE, 0, head);
+          }
+        }
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) break;
       }
     }
   } else if (warp == 5) {
@@ -288,7 +312,6 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     const int row = warp * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const float q_scale = __ldg(prm.q_scale + head * prm.q_tiles + tq) * (0.08838834764831845f * 1.4426950408889634f);
-    const float *k_scale = prm.k_scale + static_cast<int64_t>(head) * prm.kv_tiles;
     float m_used = -INFINITY;
     float l = 0.f;
     bool ok = true;
@@ -309,8 +332,10 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&sh.s_empty[b]);
 
-      const int t = dense ? j : __ldg(route_row + j);
-      const float c = q_scale * __ldg(k_scale + t);
+      // index and K scale of this tile, left in shared memory by the producer
+      // before the stage was handed to the MMA warp (stage free only after P.V(j))
+      const int t = sh.tile_index[j % kStages];
+      const float c = q_scale * sh.tile_scale[j % kStages];
       const int n_valid = min(H3S_KV_TILE, prm.sequence - t * H3S_KV_TILE);
 
       // int32 scores -> fp32 without a conversion instruction: for |s| < 2^22,
