@@ -52,7 +52,9 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
-    parser.add_argument("--config", choices=("config1", "config3"), default="config1")
+    parser.add_argument("--config", choices=("config1", "config2", "config3"), default="config1",
+                        help="config1 is the headline workload; config2 adds the chunked QKV projection in front; "
+                             "config3 is the 76112-token sequence")
     parser.add_argument("--budget", type=float, default=VIDEO_BUDGET)
     parser.add_argument("--single-term-p", action="store_true",
                         help="carry P as one E4M3 term (faster, outside the parity gate on Gaussian V)")
@@ -193,15 +195,114 @@ def workload_name(spec, budget):
                " + ".join("%d %s" % (b - a, kind) for a, b, kind in spec.segments), budget * 100))
 
 
+def run_config2(args, spec):
+    """BASELINE config 2 on one GPU: chunked ConvRot INT8 QKV projection
+    (hidden 3072 -> 3 x H x 128, 4096-token chunks) feeding the carriers, then
+    the router and the attention kernel as in config 1.  Reports the stage times
+    and the GEMM's own tensor roofline; `value` counts attention + GEMM ops."""
+    from types import SimpleNamespace
+
+    from h3_optimizations_b200 import B200SparseBackend, ChunkedSparseQKVProjector, HybridSparseConfig, ops, runtime_options
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    hidden = 3072
+    x, w, w_scale = workloads.projection_inputs(spec.sequence, hidden=hidden, heads=spec.heads, seed=0)
+    x, w, w_scale = x.to(device), w.to(device), w_scale.to(device)
+    module = SimpleNamespace(heads=spec.heads, head_dim=HEAD_DIM, qkv_weight_int8=w, qkv_weight_scale=w_scale)
+    projector = ChunkedSparseQKVProjector()
+    backend = B200SparseBackend(HybridSparseConfig(video_budget=args.budget))
+    options = runtime_options(spec.layout(), step_index=5, total_steps=30)
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    marks = []
+
+    def step(record=False):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
+        if record: e[0].record()
+        projected = projector.project(module, x, None, layer_index=0, transformer_options=options)
+        if record: e[1].record()
+        prepared = backend.prepare_projected(projected, layer_index=0, transformer_options=options)
+        if record: e[2].record()
+        out = backend.execute(prepared)
+        if record:
+            e[3].record(); marks.append(e)
+        return out, prepared.sparse
+
+    for _ in range(args.warmup):
+        _, sparse = step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0); sampler.start()
+    t0, t1 = events(); t0.record()
+    for _ in range(args.steps):
+        _, sparse = step(record=True)
+    t1.record(); torch.cuda.synchronize()
+    clocks = sampler.stop()
+    step_ms = t0.elapsed_time(t1) / args.steps
+    proj_ms = statistics.mean(m[0].elapsed_time(m[1]) for m in marks)
+    route_ms = statistics.mean(m[1].elapsed_time(m[2]) for m in marks)
+    attn_ms = statistics.mean(m[2].elapsed_time(m[3]) for m in marks)
+
+    # the GEMM alone, every chunk of the sequence, into a throw-away staging buffer
+    staging = torch.empty((3 * spec.heads, spec.sequence, HEAD_DIM), dtype=torch.bfloat16, device=device)
+    x_i8, x_scale = ops.convrot_quant_rows(x)
+    chunks = [(a, min(a + 4096, spec.sequence)) for a in range(0, spec.sequence, 4096)]
+    def gemm_all():
+        for a, b in chunks:
+            ops.qkv_gemm_chunk(x_i8[a:b], x_scale[a:b], w, w_scale, staging, row_start=a)
+    for _ in range(3): gemm_all()
+    g0, g1 = events(); g0.record()
+    for _ in range(args.steps): gemm_all()
+    g1.record(); torch.cuda.synchronize()
+    gemm_ms = g0.elapsed_time(g1) / args.steps
+    c0, c1 = events(); c0.record()
+    for _ in range(args.steps): ops.convrot_quant_rows(x, x_i8, x_scale)
+    c1.record(); torch.cuda.synchronize()
+    rot_ms = c0.elapsed_time(c1) / args.steps
+
+    geo = sparse.route.geometry
+    attn_ops = float(attention_ops(spec, sparse.route.indices, geo, spec.heads))
+    gemm_ops = 2.0 * spec.sequence * hidden * 3 * spec.heads * HEAD_DIM
+    peaks, peak_source = measured_peaks()
+    int8_peak = 2.0 * float(peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))
+    gemm_tops = gemm_ops / (gemm_ms * 1e-3) / 1e12
+    rot_bytes = spec.sequence * hidden * 3 + spec.sequence * 4
+    line = {
+        "metric": METRIC, "value": (attn_ops + gemm_ops) / (step_ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 GEMM + int8 QK^T / fp8-e4m3 PV", "data": "synthetic",
+        "config": {"workload": "config2: x (%d,%d) bf16 -> ConvRot INT8 QKV projection (W %dx%d int8, 4096-token chunks) -> %s"
+                               % (spec.sequence, hidden, 3 * spec.heads * HEAD_DIM, hidden, workload_name(spec, args.budget)),
+                   "algorithmic_ops": {"attention": attn_ops, "qkv_gemm": gemm_ops},
+                   "l2_policy": "activations + staging (>800 MB) exceed the 126 MB L2; no flush"},
+        "stages_ms": {"projection (rotate+gemm+carriers)": proj_ms, "router": route_ms, "attention": attn_ms,
+                      "qkv_gemm alone": gemm_ms, "convrot alone": rot_ms},
+        "roofline": {"bound": "tensor", "kernel": "qkv_gemm_kernel", "achieved": gemm_tops, "peak": int8_peak,
+                     "unit": "TOP/s", "frac": gemm_tops / int8_peak, "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS,
+                     "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s)" % peak_source, "traffic": None},
+        "convrot_hbm": {"bytes": rot_bytes, "gbs": rot_bytes / (rot_ms * 1e-3) / 1e9,
+                        "frac_of_measured_copy": rot_bytes / (rot_ms * 1e-3) / 1e9 / float(peaks["hbm_gbs"])},
+        "clocks": clocks, "gpu_launches": args.steps * (len(chunks) * 3 + 6),
+    }
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
-    spec = {"config1": workloads.CONFIG1, "config3": workloads.CONFIG3}[args.config]
+    spec = {"config1": workloads.CONFIG1, "config2": workloads.CONFIG1, "config3": workloads.CONFIG3}[args.config]
     if args.heads:
         import dataclasses
 
         spec = dataclasses.replace(spec, heads=args.heads, name="%s[%d heads]" % (spec.name, args.heads))
     if args.impl == "reference":
         run_reference(args, spec)
+        return
+    if args.config == "config2":
+        if args.gpus != 1:
+            raise SystemExit("config2 is a single-GPU stage benchmark here; use --gpus 1")
+        run_config2(args, spec)
         return
 
     import torch.distributed as dist
