@@ -308,7 +308,7 @@ def main():
     import torch.distributed as dist
 
     from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, ops, runtime_options
-    from h3_optimizations_b200.sharding import gather_heads, head_partition
+    from h3_optimizations_b200.sharding import SymmetricHeadOutput, gather_heads, head_partition
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -318,6 +318,8 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        # plain peer stores only: the symmetric allocation needs no NVLink multicast binding
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         dist.init_process_group("nccl", device_id=device)
 
     h0, h1 = head_partition(spec.heads, world, rank)
@@ -325,7 +327,24 @@ def main():
     q, k, v = (t.to(device, non_blocking=True) for t in (q_host, k_host, v_host))
     backend = B200SparseBackend(HybridSparseConfig(video_budget=args.budget))
     options = runtime_options(spec.layout(), step_index=5, total_steps=30)
-    full_out = torch.empty((1, spec.heads, spec.sequence, HEAD_DIM), dtype=torch.bfloat16, device=device) if world > 1 else None
+    full_out, symmetric, peer_ptrs, exchange = None, None, None, "none"
+    if world > 1:
+        try:
+            if os.environ.get("H3S_BENCH_NCCL_GATHER"):
+                raise RuntimeError("NCCL gather requested")
+            symmetric = SymmetricHeadOutput(spec.heads, spec.sequence, torch.bfloat16, device)
+            full_out, peer_ptrs = symmetric.tensor, symmetric.peer_slice_ptrs()
+            exchange = "attention epilogue stores every tile into all peers' buffers (P2P over NVLink) + barrier"
+        except Exception as exc:  # symmetric memory unavailable: plain NCCL all-gather after the kernel
+            symmetric = None
+            failure = exc
+        agreed = torch.tensor([1 if symmetric is not None else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:  # all ranks take the same path
+            exc = failure if symmetric is None else RuntimeError("a peer could not set up symmetric memory")
+            symmetric, peer_ptrs = None, None
+            full_out = torch.empty((1, spec.heads, spec.sequence, HEAD_DIM), dtype=torch.bfloat16, device=device)
+            exchange = "NCCL all-gather after the kernel (%s)" % str(exc).splitlines()[0][:80]
 
     attn_events = []
     prep_events = []
@@ -343,7 +362,7 @@ def main():
             out = ops.sparse_attention(
                 sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale, sparse.v_scale,
                 sparse.route.indices, q_start=geo.pure_video_q_start, q_stop=geo.pure_video_q_stop, out=local,
-                single_term_p=args.single_term_p)
+                single_term_p=args.single_term_p, peer_out_ptrs=peer_ptrs)
         else:
             out = ops.sparse_attention(
                 sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale, sparse.v_scale,
@@ -353,13 +372,27 @@ def main():
             e2 = torch.cuda.Event(enable_timing=True); e2.record()
             prep_events.append((e0, e1)); attn_events.append((e1, e2))
         if world > 1:
-            out = gather_heads(out, spec.heads, out=full_out)
+            if symmetric is not None:
+                symmetric.barrier()
+                out = full_out
+            else:
+                out = gather_heads(out, spec.heads, out=full_out)
         return out, sparse
 
     def fence():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- the fused scatter must reproduce what an NCCL all-gather of the local outputs gives ----
+    if symmetric is not None:
+        step(q, k, v)
+        torch.cuda.synchronize()
+        reference = gather_heads(full_out[:, h0:h1].clone(), spec.heads)
+        torch.cuda.synchronize()
+        if not torch.equal(reference, full_out):
+            raise SystemExit("rank %d: peer-scattered output differs from the NCCL all-gather" % rank)
+        dist.barrier()
 
     # ---- device-resident timing ----
     sparse = None
@@ -427,7 +460,7 @@ def main():
             "data": "synthetic",
             "config": {
                 "workload": workload_name(spec, args.budget),
-                "heads_per_gpu": h1 - h0, "parallelism": "head-sharded x%d" % world,
+                "heads_per_gpu": h1 - h0, "parallelism": "head-sharded x%d" % world, "exchange": exchange,
                 "l2_policy": "inputs (Q,K,V bf16 = %.0f MB per GPU) exceed the 126 MB L2; no flush"
                              % ((h1 - h0) * spec.sequence * HEAD_DIM * 2 * 3 / 1e6),
                 "p_terms": 1 if args.single_term_p else 2,

@@ -57,6 +57,9 @@ PROTOTYPES = {
     "h3s_sparse_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                     c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int64, c_int64,
                                     c_int, c_int, c_int, c_void_p, c_void_p]),
+    "h3s_sparse_attn_fwd_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
+                                            c_int64, c_int64, c_int, c_int, c_int, c_void_p, c_void_p]),
     "h3s_sparse_attn_fwd_mma": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int64,
                                         c_int64, c_int, c_int, c_int, c_void_p]),

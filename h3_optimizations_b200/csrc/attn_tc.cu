@@ -61,6 +61,11 @@ struct AttnParams {
   int route_len, q_start, q_stop;
   int heads, sequence, q_tiles, kv_tiles;
   int out_dtype;
+  // head-sharded runs: every output tile is also stored into these buffers
+  // (the same slice of each peer GPU's full output, reached over NVLink with
+  // plain stores), so no separate gather pass is needed
+  void *peer_out[H3S_MAX_PEER_OUTPUTS];
+  int n_peer_out;
 };
 
 struct AttnShared {
@@ -457,6 +462,11 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
             for (int e = 0; e < 8; ++e)
               v[e] = __uint_as_float(o[i + e]) * sh.v_scale[cc * 32 + i + e] * inv_l;
             store_out8<OutT>(orow + cc * 32 + i, v);
+            for (int peer = 0; peer < prm.n_peer_out; ++peer) {
+              OutT *prow = static_cast<OutT *>(prm.peer_out[peer]) + head * prm.out_stride_h +
+                           static_cast<int64_t>(grow) * prm.out_stride_s;
+              store_out8<OutT>(prow + cc * 32 + i, v);
+            }
           }
         }
       }
@@ -525,13 +535,19 @@ int check_attn_args(const int8_t *q8, const int8_t *k8, const uint8_t *v8t, cons
 
 }  // namespace h3s
 
-extern "C" int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
-                                   const float *q_scale, const float *k_scale, const float *v_scale,
-                                   const int32_t *route, int route_len, int q_start, int q_stop,
-                                   void *out, int out_dtype, int64_t out_stride_h, int64_t out_stride_s,
-                                   int heads, int sequence, int flags, int32_t *status,
-                                   h3s_stream_t stream) {
-  using namespace h3s;
+namespace h3s {
+static int sparse_attn_fwd_impl(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
+                                const float *q_scale, const float *k_scale, const float *v_scale,
+                                const int32_t *route, int route_len, int q_start, int q_stop,
+                                void *out, void *const *peer_out, int n_peer_out, int out_dtype,
+                                int64_t out_stride_h, int64_t out_stride_s,
+                                int heads, int sequence, int flags, int32_t *status,
+                                h3s_stream_t stream) {
+  H3S_CHECK_ARG(n_peer_out >= 0 && n_peer_out <= H3S_MAX_PEER_OUTPUTS && (n_peer_out == 0 || peer_out != nullptr),
+                "sparse_attn_fwd: %d peer outputs (at most %d)", n_peer_out, H3S_MAX_PEER_OUTPUTS);
+  for (int i = 0; i < n_peer_out; ++i)
+    H3S_CHECK_ARG(peer_out[i] != nullptr && (reinterpret_cast<uintptr_t>(peer_out[i]) & 15) == 0,
+                  "sparse_attn_fwd: peer output %d is NULL or not 16-byte aligned", i);
   {
     int rc = check_attn_args(q8, k8, v8t, q_scale, k_scale, v_scale, route, route_len, q_start, q_stop, out,
                              out_dtype, out_stride_h, out_stride_s, heads, sequence, "sparse_attn_fwd");
@@ -562,6 +578,8 @@ extern "C" int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uin
   prm.heads = heads; prm.sequence = sequence;
   prm.q_tiles = ceil_div(sequence, H3S_Q_TILE); prm.kv_tiles = ceil_div(sequence, H3S_KV_TILE);
   prm.out_dtype = out_dtype;
+  prm.n_peer_out = n_peer_out;
+  for (int i = 0; i < H3S_MAX_PEER_OUTPUTS; ++i) prm.peer_out[i] = i < n_peer_out ? peer_out[i] : nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool split_p = (flags & H3S_ATTN_P_SINGLE) == 0;
   switch (out_dtype) {
@@ -569,4 +587,27 @@ extern "C" int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uin
     case H3S_BF16: return launch_attn_tc<__nv_bfloat16>(mq, mk, mv, prm, split_p, s);
     default: return launch_attn_tc<__half>(mq, mk, mv, prm, split_p, s);
   }
+}
+}  // namespace h3s
+
+extern "C" int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
+                                   const float *q_scale, const float *k_scale, const float *v_scale,
+                                   const int32_t *route, int route_len, int q_start, int q_stop,
+                                   void *out, int out_dtype, int64_t out_stride_h, int64_t out_stride_s,
+                                   int heads, int sequence, int flags, int32_t *status,
+                                   h3s_stream_t stream) {
+  return h3s::sparse_attn_fwd_impl(q8, k8, v8t, q_scale, k_scale, v_scale, route, route_len, q_start, q_stop, out,
+                                   nullptr, 0, out_dtype, out_stride_h, out_stride_s, heads, sequence, flags,
+                                   status, stream);
+}
+
+extern "C" int h3s_sparse_attn_fwd_scatter(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
+                                           const float *q_scale, const float *k_scale, const float *v_scale,
+                                           const int32_t *route, int route_len, int q_start, int q_stop,
+                                           void *out, void *const *peer_out, int n_peer_out, int out_dtype,
+                                           int64_t out_stride_h, int64_t out_stride_s, int heads, int sequence,
+                                           int flags, int32_t *status, h3s_stream_t stream) {
+  return h3s::sparse_attn_fwd_impl(q8, k8, v8t, q_scale, k_scale, v_scale, route, route_len, q_start, q_stop, out,
+                                   peer_out, n_peer_out, out_dtype, out_stride_h, out_stride_s, heads, sequence,
+                                   flags, status, stream);
 }

@@ -71,10 +71,11 @@ convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride,
     amax = warp_amax[0];
     for (int w = 1; w < groups; ++w) amax = fmaxf(amax, warp_amax[w]);
     const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    const SharedDivisor by_scale = make_divisor(scale);  // exact v/scale without a divide per element
     uint32_t packed[2] = {0u, 0u};
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      int code = __float2int_rn(__fdiv_rn(v[i], scale));
+      int code = __float2int_rn(divide(by_scale, v[i]));
       code = max(-127, min(127, code));
       packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
     }

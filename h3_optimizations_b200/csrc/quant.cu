@@ -89,31 +89,6 @@ __global__ void column_stats_finalize_kernel(const double *__restrict__ k_sum,
   }
 }
 
-// Correctly rounded a/b for many a and one b: with r = RN(1/b),
-//   q0 = RN(a*r), e = a - b*q0 (exact in an FMA), q = RN(q0 + e*r)
-// equals RN(a/b) (Markstein) unless b's significand is all ones, where RN(1/b)
-// is not accurate enough; `exact` is false there and the IEEE divide is used.
-struct SharedDivisor {
-  float b, r;
-  bool exact;
-};
-
-__device__ __forceinline__ SharedDivisor make_divisor(float divisor) {
-  SharedDivisor d;
-  d.b = divisor;
-  d.r = __frcp_rn(divisor);
-  d.exact = (__float_as_uint(divisor) & 0x007fffffu) != 0x007fffffu && fabsf(divisor) > 1.0e-30f &&
-            fabsf(divisor) < 1.0e30f;
-  return d;
-}
-
-__device__ __forceinline__ float divide(const SharedDivisor &d, float a) {
-  if (!d.exact) return __fdiv_rn(a, d.b);
-  const float q0 = __fmul_rn(a, d.r);
-  const float e = __fmaf_rn(-d.b, q0, a);
-  return __fmaf_rn(e, d.r, q0);
-}
-
 // ---------------------------------------------------------------------------
 // Per-block INT8 quantisation with optional tile means.
 // One CTA = one (block, head); the whole block lives in registers, as loaded

@@ -297,9 +297,13 @@ def new_attention_output(heads, sequence, dtype, device):
 
 
 def sparse_attention(q8, k8, v_carrier, q_scale, k_scale, v_scale, route=None, *, q_start=0, q_stop=0,
-                     out=None, out_dtype=torch.bfloat16, status=None, legacy_mma=False, single_term_p=False):
+                     out=None, out_dtype=torch.bfloat16, status=None, legacy_mma=False, single_term_p=False,
+                     peer_out_ptrs=None):
     """Launch the attention kernel.  Returns ``out`` (HND).  ``single_term_p``
-    carries the probabilities as one E4M3 term instead of hi + lo."""
+    carries the probabilities as one E4M3 term instead of hi + lo.
+    ``peer_out_ptrs``: device addresses (ints) of up to 7 further buffers,
+    addressed like ``out``, that receive every output tile as well (the slices
+    of the peer GPUs' full outputs in a head-sharded run)."""
     lib = _native.load()
     if out is None:
         out = new_attention_output(q8.shape[1], q8.shape[2], out_dtype, q8.device)
@@ -309,6 +313,16 @@ def sparse_attention(q8, k8, v_carrier, q_scale, k_scale, v_scale, route=None, *
         int(q_start), int(q_stop), ptr(out), dtype_code(out.dtype), out.stride(1), out.stride(2), heads, sequence,
     )
     flags = ATTN_P_SINGLE if single_term_p else 0
+    if peer_out_ptrs:
+        if legacy_mma:
+            raise _native.NativeError("sparse_attention: the cross-check kernel does not scatter to peers")
+        table = (ctypes.c_void_p * len(peer_out_ptrs))(*[ctypes.c_void_p(int(p)) for p in peer_out_ptrs])
+        check(
+            lib.h3s_sparse_attn_fwd_scatter(*common[:11], table, len(peer_out_ptrs), *common[11:], flags,
+                                            ptr(status), stream_ptr(q8.device)),
+            "h3s_sparse_attn_fwd_scatter",
+        )
+        return out
     if legacy_mma:
         check(lib.h3s_sparse_attn_fwd_mma(*common, flags, stream_ptr(q8.device)), "h3s_sparse_attn_fwd_mma")
     else:

@@ -55,3 +55,46 @@ def gather_heads(local_out, heads, group=None, out=None):
         a, b = head_partition(heads, world, r)
         out[0, a:b] = piece[: b - a]
     return out
+
+
+class SymmetricHeadOutput:
+    """Full ``(1, heads, S, 128)`` attention output living in symmetric memory,
+    so that every rank can store its heads' tiles straight into every peer's
+    copy (``ops.sparse_attention(..., peer_out_ptrs=...)``): the attention
+    kernel then does the all-gather itself over NVLink and only a barrier is
+    left.  Construction is collective.  Raises ``RuntimeError`` when symmetric
+    memory is not available; callers then fall back to ``gather_heads``."""
+
+    def __init__(self, heads, sequence, dtype, device, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.heads, self.sequence = int(heads), int(sequence)
+        if self.world - 1 > 7:
+            raise RuntimeError("at most 8 ranks can scatter to each other")
+        numel = self.heads * self.sequence * 128
+        self._flat = symm_mem.empty((numel,), dtype=dtype, device=device)
+        self._handle = symm_mem.rendezvous(self._flat, self.group)
+        self.tensor = self._flat.view(1, self.heads, self.sequence, 128)
+        ptrs = [int(p) for p in self._handle.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != self._flat.data_ptr():
+            raise RuntimeError("symmetric memory rendezvous returned an unexpected pointer table")
+        self._ptrs = ptrs
+        self._head_bytes = self.sequence * 128 * self._flat.element_size()
+
+    def local_slice(self):
+        a, b = head_partition(self.heads, self.world, self.rank)
+        return self.tensor[:, a:b]
+
+    def peer_slice_ptrs(self):
+        """Device addresses of this rank's head slice inside every peer's buffer."""
+        a, _ = head_partition(self.heads, self.world, self.rank)
+        return [p + a * self._head_bytes for r, p in enumerate(self._ptrs) if r != self.rank]
+
+    def barrier(self):
+        """Stream-ordered barrier across the ranks: once it has passed, every
+        peer's stores into this rank's buffer (issued before their barrier) are
+        visible here."""
+        self._handle.barrier()

@@ -211,6 +211,7 @@ int h3s_route_to_delta_lut(const int32_t *route, int heads, int q_tiles,
 /* Attention ------------------------------------------------------------- */
 
 #define H3S_ATTN_P_SINGLE 1
+#define H3S_MAX_PEER_OUTPUTS 7
 
 /*
  * Block-sparse attention on the carriers (tcgen05 kind::i8 QK^T into TMEM,
@@ -235,6 +236,29 @@ int h3s_sparse_attn_fwd(const int8_t *q8, const int8_t *k8, const uint8_t *v8t,
                         int out_dtype, int64_t out_stride_h,
                         int64_t out_stride_s, int heads, int sequence,
                         int flags, int32_t *status, h3s_stream_t stream);
+
+/*
+ * h3s_sparse_attn_fwd for head-sharded runs (one process per GPU, this rank
+ * holds `heads` of the layer's heads): besides `out`, every output tile is
+ * stored with plain peer-to-peer stores into `n_peer_out` (<= 7) further
+ * buffers - the slice of each peer GPU's full (H_total,S,128) output that
+ * belongs to this rank's heads, mapped into this process (e.g. CUDA IPC or
+ * torch symmetric memory) and addressed with the same strides as `out`.  The
+ * attention kernel thereby performs the all-gather of the head-sharded output
+ * itself, tile by tile over NVLink; the caller only needs a cross-rank barrier
+ * before a peer reads its buffer.  No TMA, no multicast touches peer memory.
+ * (No counterpart in the reference, which is single-GPU.)
+ */
+int h3s_sparse_attn_fwd_scatter(const int8_t *q8, const int8_t *k8,
+                                const uint8_t *v8t, const float *q_scale,
+                                const float *k_scale, const float *v_scale,
+                                const int32_t *route, int route_len,
+                                int q_start, int q_stop, void *out,
+                                void *const *peer_out, int n_peer_out,
+                                int out_dtype, int64_t out_stride_h,
+                                int64_t out_stride_s, int heads, int sequence,
+                                int flags, int32_t *status,
+                                h3s_stream_t stream);
 
 /*
  * Same contract, legacy tensor path (mma.sync m16n8k32 s8 / e4m3).  Kept as
