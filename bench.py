@@ -320,6 +320,9 @@ def main():
     if world > 1:
         # plain peer stores only: the symmetric allocation needs no NVLink multicast binding
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        # stdout carries exactly one JSON line: keep NCCL's version banner out of it
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("VERSION", "INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     h0, h1 = head_partition(spec.heads, world, rank)

@@ -444,33 +444,59 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ok = warp_wait(&sh.p_empty[last & 1], static_cast<uint32_t>(last >> 1) & 1u, abort_word, kAbortFinal);
     }
     if (ok) {
+      // Epilogue: O * v_scale / l -> OutT, staged through shared memory (the K
+      // stage ring is free: every TMA load has been consumed) so that each warp
+      // writes its 32 rows as full contiguous lines - to the local output and,
+      // in a head-sharded run, to the same slice of every peer GPU's output
+      // (plain stores over NVLink).  A warp only reads back the rows it staged
+      // itself, so __syncwarp is the only synchronisation.
       ptx::tc_fence_after();
       const float inv_l = 1.0f / l;
-      const int grow = tq * H3S_Q_TILE + row;
-      OutT *orow = static_cast<OutT *>(prm.out) + head * prm.out_stride_h +
-                   static_cast<int64_t>(grow) * prm.out_stride_s;
+      constexpr int kRowBytes = H3S_HEAD_DIM * static_cast<int>(sizeof(OutT));
+      constexpr int kChunksPerRow = kRowBytes / 16;
+      unsigned char *stage = smem + kOffK;
+      static_assert(H3S_Q_TILE * kRowBytes <= kStages * (kKBytes + kVBytes), "output tile must fit the stage ring");
+      unsigned char *my_row = stage + row * kRowBytes;
 #pragma unroll 1
       for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
         uint32_t o[32];
         H3S_TMEM_LD32(tmem_o + lane_addr + cc * 32, o);
         ptx::tmem_wait_ld();
-        if (grow < prm.sequence) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            float v[8];
+        for (int i = 0; i < 32; i += 8) {
+          float v[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              v[e] = __uint_as_float(o[i + e]) * sh.v_scale[cc * 32 + i + e] * inv_l;
-            store_out8<OutT>(orow + cc * 32 + i, v);
-            for (int peer = 0; peer < prm.n_peer_out; ++peer) {
-              OutT *prow = static_cast<OutT *>(prm.peer_out[peer]) + head * prm.out_stride_h +
-                           static_cast<int64_t>(grow) * prm.out_stride_s;
-              store_out8<OutT>(prow + cc * 32 + i, v);
-            }
-          }
+          for (int e = 0; e < 8; ++e)
+            v[e] = __uint_as_float(o[i + e]) * sh.v_scale[cc * 32 + i + e] * inv_l;
+          // 8 values = one (bf16/fp16) or two (fp32) 16-byte chunks; the chunk index is
+          // XORed with the row so that the 32 rows of a warp do not collide on banks
+          constexpr int kChunks8 = 8 * static_cast<int>(sizeof(OutT)) / 16;
+          const int chunk0 = (cc * 32 + i) * static_cast<int>(sizeof(OutT)) / 16;
+          __align__(16) OutT tmp[8];
+          store_out8<OutT>(tmp, v);
+#pragma unroll
+          for (int k = 0; k < kChunks8; ++k)
+            *reinterpret_cast<uint4 *>(my_row + (((chunk0 + k) ^ (row & 15)) << 4)) =
+                reinterpret_cast<const uint4 *>(tmp)[k];
         }
       }
       ptx::tc_fence_before();
+      __syncwarp();
+      const int warp_row0 = warp * 32;
+      for (int dest = 0; dest <= prm.n_peer_out; ++dest) {
+        unsigned char *base = static_cast<unsigned char *>(dest == 0 ? prm.out : prm.peer_out[dest - 1]);
+#pragma unroll 4
+        for (int idx = lane; idx < 32 * kChunksPerRow; idx += 32) {
+          const int r = warp_row0 + idx / kChunksPerRow, c = idx % kChunksPerRow;
+          const int grow = tq * H3S_Q_TILE + r;
+          if (grow < prm.sequence) {
+            const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * kRowBytes + ((c ^ (r & 15)) << 4));
+            unsigned char *dst = base + (head * prm.out_stride_h + static_cast<int64_t>(grow) * prm.out_stride_s) *
+                                            static_cast<int64_t>(sizeof(OutT)) + c * 16;
+            *reinterpret_cast<uint4 *>(dst) = value;
+          }
+        }
+      }
     }
   }
 

@@ -95,6 +95,30 @@ def test_output_types_strides_and_determinism(ops):
     assert m["cosine"] >= TIGHT_COS and m["rel_max_abs"] <= 2e-2, m
 
 
+def test_scatter_entry_writes_every_extra_buffer(ops):
+    """The head-sharded entry point stores each output tile into further
+    buffers as well (on a multi-GPU box: the peers' copies, over NVLink).  Here
+    the extra buffers live on the same device, which exercises the same code."""
+    spec = workloads.small_spec("att", 2, 100, 441)  # 541 tokens: ragged last query tile
+    q, k, v = workloads.gaussian_qkv(spec, seed=7, widen=True)
+    geo, retained, selected, route = oracle.build_route(q, k, 541, 100, 0.4)
+    carriers = _carriers(q, k, v)
+    for dtype in (torch.bfloat16, torch.float32):
+        plain = _run(ops, carriers, route, geo, out_dtype=dtype)
+        # three "peer" buffers holding 5 heads each; this rank owns heads 2 and 3 of them
+        peers = [torch.full((1, 5, 541, 128), float("nan"), dtype=dtype, device="cuda") for _ in range(3)]
+        local = torch.empty((1, 2, 541, 128), dtype=dtype, device="cuda")
+        slice_ptrs = [p[:, 2:4].data_ptr() for p in peers]
+        got = _run(ops, carriers, route, geo, out=local, peer_out_ptrs=slice_ptrs)
+        assert torch.equal(got, plain.contiguous())
+        for p in peers:
+            assert torch.equal(p[:, 2:4], plain.contiguous())
+            assert bool(torch.isnan(p[:, :2].float()).all()) and bool(torch.isnan(p[:, 4:].float()).all())
+    from h3_optimizations_b200._native import NativeError
+    with pytest.raises(NativeError, match="at most 7"):
+        _run(ops, carriers, route, geo, out_dtype=torch.bfloat16, peer_out_ptrs=[local.data_ptr()] * 8)
+
+
 def test_video_first_layout(ops):
     spec = workloads.CONFIG0_VIDEO_FIRST
     q, k, v = workloads.gaussian_qkv(spec, seed=0, widen=True)
