@@ -46,7 +46,7 @@ constexpr float kPOffset = 5.0f;
 constexpr float kIntBias = 12582912.0f;  // 1.5 * 2^23: float(kIntBias + s) has bits 0x4b400000 + s
 
 enum AbortCode {
-  kAbortQFull = 1, kAbortKvFull, kAbortKvEmpty, kAbortSFull, kAbortSEmpty, kAbortPFull, kAbortPEmpty,
+  kAbortQFull = 1, kAbortKvFull, kAbortKvEmpty, kAbortSFull, kAbortPFull, kAbortPEmpty,
   kAbortPvDone, kAbortFinal
 };
 
@@ -73,7 +73,6 @@ struct AttnShared {
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
   uint64_t s_full[2];
-  uint64_t s_empty[2];
   uint64_t p_full[2];
   uint64_t p_empty[2];
   uint32_t tmem_base;
@@ -209,7 +208,6 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&sh.s_full[i], 1);
-      ptx::mbar_init(&sh.s_empty[i], 4);
       ptx::mbar_init(&sh.p_full[i], 4);
       ptx::mbar_init(&sh.p_empty[i], 1);
     }
@@ -274,42 +272,57 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       constexpr uint32_t idesc_qk = ptx::umma_idesc(2, 1, 1, H3S_Q_TILE, H3S_KV_TILE);
       constexpr uint32_t idesc_pv = ptx::umma_idesc(1, 0, 0, H3S_Q_TILE, H3S_HEAD_DIM);
       const uint32_t q_addr = ptx::smem_u32(smem + kOffQ);
+      // Issue order: QK(0), QK(1), then for every tile i: P.V(i), QK(i+2).
+      // QK(i+2) overwrites S buffer i&1, which holds P(i) until P.V(i) has
+      // read it; MMAs of one thread execute in issue order, so placing it
+      // right behind P.V(i) is enough, and p_full(i) already says that the
+      // softmax warps are done with S(i).  The K/V stage of tile i+2 is waited
+      // for BEFORE p_full(i) so that nothing sits between the arrival of P(i)
+      // and the two MMA groups that depend on it.
+      auto issue_qk = [&](int j) {
+        const int s = j % kStages, b = j & 1;
+        const uint64_t a_desc = ptx::umma_desc_kmajor(q_addr, 1024, ptx::kSwizzle128);
+        const uint64_t b_desc =
+            ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffK + s * kKBytes), 1024, ptx::kSwizzle128);
+#pragma unroll
+        for (int k = 0; k < H3S_HEAD_DIM / 32; ++k)
+          ptx::umma_i8(tmem_s + b * H3S_KV_TILE, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, k > 0);
+        ptx::tc_commit(&sh.s_full[b]);
+      };
+      auto wait_stage = [&](int j) {
+        return ptx::mbar_wait(&sh.kv_full[j % kStages], static_cast<uint32_t>(j / kStages) & 1u, abort_word,
+                              kAbortKvFull);
+      };
       bool ok = ptx::mbar_wait(&sh.q_full, 0, abort_word, kAbortQFull);
-      for (int j = 0; ok && j <= n_iter; ++j) {
-        if (j < n_iter) {
-          const int s = j % kStages, b = j & 1;
-          const uint32_t kv_use = static_cast<uint32_t>(j / kStages), s_use = static_cast<uint32_t>(j >> 1);
-          if (!ptx::mbar_wait(&sh.kv_full[s], kv_use & 1u, abort_word, kAbortKvFull)) { ok = false; break; }
-          if (!ptx::mbar_wait(&sh.s_empty[b], (s_use & 1u) ^ 1u, abort_word, kAbortSEmpty)) { ok = false; break; }
+      for (int j = 0; ok && j < min(2, n_iter); ++j) {
+        ok = wait_stage(j);
+        if (ok) {
           ptx::tc_fence_after();
-          const uint64_t a_desc = ptx::umma_desc_kmajor(q_addr, 1024, ptx::kSwizzle128);
-          const uint64_t b_desc =
-              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffK + s * kKBytes), 1024, ptx::kSwizzle128);
-#pragma unroll
-          for (int k = 0; k < H3S_HEAD_DIM / 32; ++k)
-            ptx::umma_i8(tmem_s + b * H3S_KV_TILE, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, k > 0);
-          ptx::tc_commit(&sh.s_full[b]);
+          issue_qk(j);
         }
-        if (j > 0) {
-          const int i = j - 1;
-          const int s = i % kStages, b = i & 1;
-          const uint32_t p_use = static_cast<uint32_t>(i >> 1);
-          if (!ptx::mbar_wait(&sh.p_full[b], p_use & 1u, abort_word, kAbortPFull)) { ok = false; break; }
-          ptx::tc_fence_after();
-          const uint64_t b_desc =
-              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV + s * kVBytes), 512, ptx::kSwizzle64);
-          // P(i) sits in TMEM on top of S buffer b: columns [0,16) hi, [16,32) lo,
-          // four E4M3 per column, 8 columns per K=32 step
-#pragma unroll
-          for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
-#pragma unroll
-            for (int k = 0; k < H3S_KV_TILE / 32; ++k)
-              ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, b_desc + 2 * k, idesc_pv,
-                              (i > 0 || k > 0 || term > 0) ? 1u : 0u);
-          }
-          ptx::tc_commit(&sh.kv_empty[s]);
-          ptx::tc_commit(&sh.p_empty[b]);
+      }
+      for (int i = 0; ok && i < n_iter; ++i) {
+        const int s = i % kStages, b = i & 1;
+        if (i + 2 < n_iter && !wait_stage(i + 2)) { ok = false; break; }
+        if (!ptx::mbar_wait(&sh.p_full[b], static_cast<uint32_t>(i >> 1) & 1u, abort_word, kAbortPFull)) {
+          ok = false;
+          break;
         }
+        ptx::tc_fence_after();
+        const uint64_t b_desc =
+            ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV + s * kVBytes), 512, ptx::kSwizzle64);
+        // P(i) sits in TMEM on top of S buffer b: columns [0,16) hi, [16,32) lo,
+        // four E4M3 per column, 8 columns per K=32 step
+#pragma unroll
+        for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
+#pragma unroll
+          for (int k = 0; k < H3S_KV_TILE / 32; ++k)
+            ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, b_desc + 2 * k, idesc_pv,
+                            (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+        }
+        ptx::tc_commit(&sh.kv_empty[s]);
+        ptx::tc_commit(&sh.p_empty[b]);
+        if (i + 2 < n_iter) issue_qk(i + 2);
       }
     }
   } else {
@@ -333,9 +346,6 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         H3S_TMEM_LD32(tmem_s + lane_addr + b * H3S_KV_TILE + 32, s_hi);
       }
       ptx::tmem_wait_ld();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&sh.s_empty[b]);
 
       // index and K scale of this tile, left in shared memory by the producer
       // before the stage was handed to the MMA warp (stage free only after P.V(j))
@@ -356,14 +366,20 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         for (int i = 0; i < 64; ++i)
           if (i >= n_valid) f[i] = -INFINITY;
       }
-#ifdef H3S_PROBE_NOMAX  // timing probe only: wrong results after the first tile
-      float fm = j == 0 ? fmaxf(max3(f[0], f[1], f[2]), f[3]) + 40.f - kIntBias : -1.0e30f;
-#else
-      float fm = max3(f[0], f[1], f[2]);
+      // four independent chains of 3-input maxima (a single chain of 32 dependent
+      // instructions costs more than the arithmetic)
+      float fm0 = max3(f[0], f[1], f[2]), fm1 = max3(f[3], f[4], f[5]);
+      float fm2 = max3(f[6], f[7], f[8]), fm3 = max3(f[9], f[10], f[11]);
 #pragma unroll
-      for (int i = 3; i + 1 < 64; i += 2) fm = max3(fm, f[i], f[i + 1]);
-      fm = fmaxf(fm, f[63]) - kIntBias;
-#endif
+      for (int i = 12; i + 7 < 64; i += 8) {
+        fm0 = max3(fm0, f[i], f[i + 1]);
+        fm1 = max3(fm1, f[i + 2], f[i + 3]);
+        fm2 = max3(fm2, f[i + 4], f[i + 5]);
+        fm3 = max3(fm3, f[i + 6], f[i + 7]);
+      }
+      fm0 = max3(fm0, f[60], f[61]);
+      fm1 = max3(fm1, f[62], f[63]);
+      const float fm = max3(fm0, fm1, fmaxf(fm2, fm3)) - kIntBias;
       const float mx = c * fm;  // c > 0
       const bool need = mx > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
@@ -406,18 +422,10 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         sum2 = add2(sum2, p01);
         sum2 = add2(sum2, p23);
         if (kSplitP) {
-#ifdef H3S_PROBE_VELTKAMP
-          // hi = P rounded to 4 significant bits with FMA-pipe operations only
-          const float2 split = make_float2(1048577.f, 1048577.f);
-          const float2 g01 = mul2(p01, split), g23 = mul2(p23, split);
-          const float2 h01 = add2(g01, fma2(g01, minus1, p01));
-          const float2 h23 = add2(g23, fma2(g23, minus1, p23));
-#else
           const float2 h01 = make_float2(__uint_as_float(__float_as_uint(p01.x) & 0xfff00000u),
                                          __uint_as_float(__float_as_uint(p01.y) & 0xfff00000u));
           const float2 h23 = make_float2(__uint_as_float(__float_as_uint(p23.x) & 0xfff00000u),
                                          __uint_as_float(__float_as_uint(p23.y) & 0xfff00000u));
-#endif
           const float2 r01 = fma2(h01, minus1, p01);
           const float2 r23 = fma2(h23, minus1, p23);
           packed[i >> 2] = pack_e4m3x4(h01.x, h01.y, h23.x, h23.y);
