@@ -268,32 +268,27 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     }
   } else if (warp == 5) {
     // =================== MMA issuer ===================
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_qk = ptx::umma_idesc(2, 1, 1, H3S_Q_TILE, H3S_KV_TILE);
       constexpr uint32_t idesc_pv = ptx::umma_idesc(1, 0, 0, H3S_Q_TILE, H3S_HEAD_DIM);
-      const uint32_t q_addr = ptx::smem_u32(smem + kOffQ);
-      // Issue order: QK(0), QK(1), then for every tile i: P.V(i), QK(i+2).
-      // QK(i+2) overwrites S buffer i&1, which holds P(i) until P.V(i) has
-      // read it; MMAs of one thread execute in issue order, so placing it
-      // right behind P.V(i) is enough, and p_full(i) already says that the
-      // softmax warps are done with S(i).  The K/V stage of tile i+2 is waited
-      // for BEFORE p_full(i) so that nothing sits between the arrival of P(i)
-      // and the two MMA groups that depend on it.
+      const uint64_t q_desc = ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffQ), 1024, ptx::kSwizzle128);
+      const uint64_t k_desc0 = ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffK), 1024, ptx::kSwizzle128);
+      const uint64_t v_desc0 = ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV), 512, ptx::kSwizzle64);
       auto issue_qk = [&](int j) {
-        const int s = j % kStages, b = j & 1;
-        const uint64_t a_desc = ptx::umma_desc_kmajor(q_addr, 1024, ptx::kSwizzle128);
-        const uint64_t b_desc =
-            ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffK + s * kKBytes), 1024, ptx::kSwizzle128);
+        if (ptx::elect_one()) {
+          const uint64_t k_desc = k_desc0 + static_cast<uint64_t>((j % kStages) * (kKBytes >> 4));
 #pragma unroll
-        for (int k = 0; k < H3S_HEAD_DIM / 32; ++k)
-          ptx::umma_i8(tmem_s + b * H3S_KV_TILE, a_desc + 2 * k, b_desc + 2 * k, idesc_qk, k > 0);
-        ptx::tc_commit(&sh.s_full[b]);
+          for (int k = 0; k < H3S_HEAD_DIM / 32; ++k)
+            ptx::umma_i8(tmem_s + (j & 1) * H3S_KV_TILE, q_desc + 2 * k, k_desc + 2 * k, idesc_qk, k > 0);
+          ptx::tc_commit(&sh.s_full[j & 1]);
+        }
+        __syncwarp();
       };
       auto wait_stage = [&](int j) {
-        return ptx::mbar_wait(&sh.kv_full[j % kStages], static_cast<uint32_t>(j / kStages) & 1u, abort_word,
-                              kAbortKvFull);
+        return warp_wait(&sh.kv_full[j % kStages], static_cast<uint32_t>(j / kStages) & 1u, abort_word,
+                         kAbortKvFull);
       };
-      bool ok = ptx::mbar_wait(&sh.q_full, 0, abort_word, kAbortQFull);
+      bool ok = warp_wait(&sh.q_full, 0, abort_word, kAbortQFull);
       for (int j = 0; ok && j < min(2, n_iter); ++j) {
         ok = wait_stage(j);
         if (ok) {
@@ -304,24 +299,24 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int i = 0; ok && i < n_iter; ++i) {
         const int s = i % kStages, b = i & 1;
         if (i + 2 < n_iter && !wait_stage(i + 2)) { ok = false; break; }
-        if (!ptx::mbar_wait(&sh.p_full[b], static_cast<uint32_t>(i >> 1) & 1u, abort_word, kAbortPFull)) {
+        if (!warp_wait(&sh.p_full[b], static_cast<uint32_t>(i >> 1) & 1u, abort_word, kAbortPFull)) {
           ok = false;
           break;
         }
         ptx::tc_fence_after();
-        const uint64_t b_desc =
-            ptx::umma_desc_kmajor(ptx::smem_u32(smem + kOffV + s * kVBytes), 512, ptx::kSwizzle64);
-        // P(i) sits in TMEM on top of S buffer b: columns [0,16) hi, [16,32) lo,
-        // four E4M3 per column, 8 columns per K=32 step
+        if (ptx::elect_one()) {
+          const uint64_t v_desc = v_desc0 + static_cast<uint64_t>(s * (kVBytes >> 4));
 #pragma unroll
-        for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
+          for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
 #pragma unroll
-          for (int k = 0; k < H3S_KV_TILE / 32; ++k)
-            ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, b_desc + 2 * k, idesc_pv,
-                            (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+            for (int k = 0; k < H3S_KV_TILE / 32; ++k)
+              ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, v_desc + 2 * k, idesc_pv,
+                              (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+          }
+          ptx::tc_commit(&sh.kv_empty[s]);
+          ptx::tc_commit(&sh.p_empty[b]);
         }
-        ptx::tc_commit(&sh.kv_empty[s]);
-        ptx::tc_commit(&sh.p_empty[b]);
+        __syncwarp();
         if (i + 2 < n_iter) issue_qk(i + 2);
       }
     }

@@ -29,6 +29,23 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 
+// True in exactly one lane of a converged warp.  Code guarded by it is
+// recognised by the compiler as executed by a single thread of a uniform warp,
+// so the descriptor operands of tcgen05.mma / TMA instructions are built in
+// uniform registers instead of being moved there one by one.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t"
+      ".reg .b32 rx;\n\t"
+      ".reg .pred px;\n\t"
+      "elect.sync rx|px, 0xffffffff;\n\t"
+      "@px mov.s32 %0, 1;\n\t"
+      "}\n"
+      : "+r"(pred));
+  return pred != 0;
+}
+
 // ---- mbarrier ----------------------------------------------------------
 
 __device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
@@ -62,12 +79,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   return done != 0;
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 // Waits for the phase with the given parity.  Returns false (and raises
 // *abort_word with `code`) when the budget expires or another waiter already
 // gave up.  `abort_word` lives in shared memory.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word,
                                           int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // a phase that is already complete costs one test_wait (a try_wait with a
+  // suspend hint takes about twice as long even when it succeeds at once)
+  if (mbar_test_wait(bar, parity)) return true;
   const unsigned long long start = global_timer_ns();
   uint32_t spins = 0;
   while (true) {
@@ -254,6 +287,20 @@ __device__ __forceinline__ void umma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 __device__ __forceinline__ void tmem_wait_ld() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+
+// wait::ld that also names 32 destination registers of the load as read-write
+// operands, so every later use of them is ordered behind the wait by a data
+// dependence (the load fills them asynchronously)
+#define H3S_TMEM_WAIT_LD32(r)                                                                        \
+  asm volatile("tcgen05.wait::ld.sync.aligned;"                                                      \
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), \
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]),          \
+                 "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]),       \
+                 "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),       \
+                 "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]),       \
+                 "+r"(r[31])                                                                         \
+               :                                                                                     \
+               : "memory")
 
 __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
