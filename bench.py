@@ -432,6 +432,11 @@ def main():
         out_host = torch.empty((1, spec.heads if world > 1 else h1 - h0, spec.sequence, HEAD_DIM),
                                dtype=torch.bfloat16).pin_memory()
         def e2e_step():
+            if world == 1:
+                # the backend's host entry: H2D of head chunk c+1, kernels of chunk c and D2H of
+                # chunk c-1 overlap on three streams
+                backend.forward_host(q_host, k_host, v_host, out_host, layer_index=0, transformer_options=options)
+                return
             qd, kd, vd = (t.to(device, non_blocking=True) for t in (q_host, k_host, v_host))
             out, _ = step(qd, kd, vd)
             out_host.copy_(out, non_blocking=True)
@@ -448,6 +453,8 @@ def main():
         if world > 1:
             dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
         e2e = {"value": total_ops / (float(e2e_ms[0]) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(e2e_ms[0]),
+               "api": "B200SparseBackend.forward_host (pinned host Q/K/V in, host output back, head chunks pipelined)"
+                      if world == 1 else "pinned host Q/K/V -> prepare + attention + exchange -> host output",
                "h2d_bytes_per_step": 3 * q_host.numel() * q_host.element_size(),
                "d2h_bytes_per_step": out_host.numel() * out_host.element_size()}
 

@@ -256,7 +256,9 @@ class B200SparseBackend:
         )
         return PreparedHybrid(sparse=sparse)
 
-    def execute(self, prepared):
+    def execute(self, prepared, out=None):
+        """Run the attention kernel on prepared carriers.  ``out`` (optional) is
+        an HND ``(1, H, S, 128)`` tensor or view to write into."""
         sparse = prepared.sparse
         route = sparse.route
         geometry = route.geometry
@@ -266,13 +268,89 @@ class B200SparseBackend:
                 sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale,
                 sparse.v_scale, route.indices,
                 q_start=geometry.pure_video_q_start, q_stop=geometry.pure_video_q_stop,
-                out_dtype=out_dtype,
+                out=out, out_dtype=out_dtype,
             )
         except _native.NativeError as exc:
             raise SparseSageError(
                 "Sparse attention kernel failed: layer=%d sequence=%d heads=%d dtype=%s: %s"
                 % (sparse.layer_index, sparse.sequence, sparse.heads, sparse.output_dtype, exc)
             ) from exc
+
+    # -- host-resident activations -------------------------------------------
+
+    def forward_host(self, q, k, v, out=None, *, layer_index, transformer_options, heads_per_chunk=2):
+        """``prepare`` + ``execute`` for Q/K/V that live in (pinned) HOST memory.
+
+        Heads are independent on the whole path, so the call walks the heads in
+        chunks and overlaps three things on three streams: the host-to-device
+        copy of chunk c+1, the kernels of chunk c (on the current stream) and
+        the device-to-host copy of the output of chunk c-1.  The PCIe input copy
+        is the longest of the three, so the call takes about as long as that
+        copy alone.  Returns ``out`` (host, HND ``(1, H, S, 128)``; allocated
+        pinned when not given); it is complete once the current stream is
+        synchronised.  With a route sink installed the heads are not split (the
+        sink expects one call per layer)."""
+        if q.is_cuda or k.is_cuda or v.is_cuda:
+            raise SparseSageError("forward_host expects host tensors; use prepare/execute for device tensors")
+        if q.shape != k.shape or q.shape != v.shape or q.ndim != 4 or q.shape[0] != 1 or q.shape[3] != 128:
+            raise SparseSageError("forward_host expects equal (1, H, S, 128) Q/K/V; got %s %s %s"
+                                  % (tuple(q.shape), tuple(k.shape), tuple(v.shape)))
+        if not (q.is_contiguous() and k.is_contiguous() and v.is_contiguous()):
+            raise SparseSageError("forward_host expects contiguous HND host tensors")
+        _, heads, sequence, _ = q.shape
+        if out is None:
+            out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+        elif out.shape != q.shape or out.dtype != q.dtype or out.is_cuda or not out.is_contiguous():
+            raise SparseSageError("forward_host: out must be a contiguous host tensor shaped and typed like q")
+        recorder = (transformer_options or {}).get("h3_optimizations_attention_route")
+        whole = getattr(recorder, "sink", None) is not None
+        chunk = heads if whole else max(1, min(int(heads_per_chunk), heads))
+        bounds = [(a, min(a + chunk, heads)) for a in range(0, heads, chunk)]
+        device = torch.device("cuda", torch.cuda.current_device())
+        main = torch.cuda.current_stream(device)
+        state = self._host_pipeline(device, chunk, sequence, q.dtype, min(3, len(bounds)))
+        h2d, d2h, slots = state["h2d"], state["d2h"], state["slots"]
+        h2d.wait_stream(main)
+        d2h.wait_stream(main)
+        for index, (a, b) in enumerate(bounds):
+            slot = slots[index % len(slots)]
+            n = b - a
+            with torch.cuda.stream(h2d):
+                if index >= len(slots):
+                    h2d.wait_event(slot["computed"])  # the kernels of the chunk that used this slot are done
+                for name, src in (("q", q), ("k", k), ("v", v)):
+                    slot[name][:, :n].copy_(src[:, a:b], non_blocking=True)
+                slot["loaded"].record(h2d)
+            main.wait_event(slot["loaded"])
+            if index >= len(slots):
+                main.wait_event(slot["stored"])  # its previous output has left the device
+            prepared = self.prepare(slot["q"][:, :n], slot["k"][:, :n], slot["v"][:, :n],
+                                    layer_index=layer_index, transformer_options=transformer_options)
+            self.execute(prepared, out=slot["out"][:, :n])
+            slot["computed"].record(main)
+            with torch.cuda.stream(d2h):
+                d2h.wait_event(slot["computed"])
+                out[:, a:b].copy_(slot["out"][:, :n], non_blocking=True)
+                slot["stored"].record(d2h)
+        main.wait_stream(d2h)
+        main.wait_stream(h2d)
+        return out
+
+    def _host_pipeline(self, device, chunk, sequence, dtype, n_slots):
+        key = (device.index, int(chunk), int(sequence), dtype, int(n_slots))
+        cache = self.__dict__.setdefault("_host_pipelines", {})
+        state = cache.get(key)
+        if state is None:
+            cache.clear()  # one geometry at a time: the staging buffers are large
+            shape = (1, chunk, sequence, 128)
+            slots = []
+            for _ in range(n_slots):
+                slot = {name: torch.empty(shape, dtype=dtype, device=device) for name in ("q", "k", "v", "out")}
+                slot.update({name: torch.cuda.Event() for name in ("loaded", "computed", "stored")})
+                slots.append(slot)
+            state = {"h2d": torch.cuda.Stream(device), "d2h": torch.cuda.Stream(device), "slots": slots}
+            cache[key] = state
+        return state
 
     def reference_lut(self, prepared):
         """The route in the reference's delta-LUT encoding ``(lut, valid)``."""

@@ -82,3 +82,28 @@ def test_contract_errors(backend):
                         transformer_options=runtime_options(spec.layout()))
     assert backend.as_status()["sparse_architecture"] == "sm_100a"
     assert backend.installation_signature == backend.installation_signature
+
+
+def test_forward_host_matches_device_path(backend):
+    """The pipelined host entry (head chunks over three streams) returns what
+    prepare + execute return on device-resident tensors: heads are independent,
+    so chunking changes nothing, including a ragged last chunk and slot reuse."""
+    from h3_optimizations_b200 import runtime_options
+
+    spec = workloads.small_spec("host", 7, 256, 1024)
+    q, k, v = workloads.gaussian_qkv(spec, seed=9)
+    options = runtime_options(spec.layout(), 5, 30)
+    prepared = backend.prepare(q.cuda(), k.cuda(), v.cuda(), layer_index=0, transformer_options=options)
+    expected = backend.execute(prepared).contiguous().cpu()
+    qh, kh, vh = (t.contiguous().pin_memory() for t in (q, k, v))
+    for chunk in (2, 3, 7):
+        out = backend.forward_host(qh, kh, vh, layer_index=0, transformer_options=options, heads_per_chunk=chunk)
+        torch.cuda.synchronize()
+        assert out.is_pinned() and tuple(out.shape) == tuple(q.shape)
+        assert torch.equal(out, expected), "heads_per_chunk=%d" % chunk
+    # a second call reuses the staging slots and streams
+    again = backend.forward_host(qh, kh, vh, layer_index=0, transformer_options=options, heads_per_chunk=2)
+    torch.cuda.synchronize()
+    assert torch.equal(again, expected)
+    with pytest.raises(Exception, match="host tensors"):
+        backend.forward_host(q.cuda(), k.cuda(), v.cuda(), layer_index=0, transformer_options=options)
