@@ -96,7 +96,7 @@ __global__ void column_stats_finalize_kernel(const double *__restrict__ k_sum,
 // reduction and the store, so it is read from memory exactly once.
 // ---------------------------------------------------------------------------
 
-template <typename T, int BLOCK>
+template <typename T, int BLOCK, bool kHasMean>
 __global__ void __launch_bounds__(BLOCK * 2, (sizeof(T) == 2 ? 1024 : 512) / (BLOCK * 2))
 quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride_s,
                        const float *__restrict__ mean, int8_t *__restrict__ out,
@@ -119,7 +119,7 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
   float mu[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) mu[i] = 0.f;
-  if (mean != nullptr) {
+  if (kHasMean) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) mu[i] = __ldg(mean + head * H3S_HEAD_DIM + c0 + i);
   }
@@ -145,7 +145,7 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         col[i] = __fadd_rn(col[i], v[i]);
-        amax = fmaxf(amax, fabsf(__fsub_rn(v[i], mu[i])));
+        amax = fmaxf(amax, fabsf(kHasMean ? __fsub_rn(v[i], mu[i]) : v[i]));
       }
     }
   }
@@ -173,14 +173,21 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
     if (out != nullptr && r < valid_rows) {
       float v[8];
       Elem<T>::unpack(raw[p], v);
-      uint32_t packed[2] = {0u, 0u};
+      // code = trunc(v/scale +- 0.5): the half carries the quotient's sign bit,
+      // the four codes of a word are gathered with byte permutes
+      uint32_t code[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        float q = divide(by_scale, __fsub_rn(v[i], mu[i]));
-        q = __fadd_rn(q, q >= 0.f ? 0.5f : -0.5f);
-        const int code = static_cast<int>(q);  // truncation toward zero
-        packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+        float q = divide(by_scale, kHasMean ? __fsub_rn(v[i], mu[i]) : v[i]);
+        const float half = __uint_as_float((__float_as_uint(q) & 0x80000000u) | 0x3f000000u);
+        q = __fadd_rn(q, half);
+        code[i] = static_cast<uint32_t>(static_cast<int>(q));  // truncation toward zero
       }
+      uint32_t packed[2];
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+        packed[w] = __byte_perm(__byte_perm(code[4 * w], code[4 * w + 1], 0x0040),
+                                __byte_perm(code[4 * w + 2], code[4 * w + 3], 0x0040), 0x5410);
       *reinterpret_cast<uint2 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) =
           make_uint2(packed[0], packed[1]);
     }
@@ -237,6 +244,7 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
 
   float sc[8], rc[8];
   bool all_exact = true;
+  const bool clamp = v_bound < 448.0f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     sc[i] = fmaxf(__ldg(v_scale + head * H3S_HEAD_DIM + c0 + i), 1.0e-20f);
@@ -249,9 +257,9 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
 #pragma unroll
   for (int p = 0; p < kVTile / (kVThreads / 16 * 4); ++p) {
     const int r0 = (p * (kVThreads / 16) + slot) * 4;  // four consecutive rows
-    uint32_t word[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) word[i] = 0u;
+    // four consecutive rows of 8 channels -> per channel one word of four codes
+    // (two 2-wide conversions and one byte permute)
+    float q[4][8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       if (r0 + j < valid_rows) {
@@ -259,18 +267,27 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
         Elem<T>::load8(base + static_cast<int64_t>(first_row + r0 + j) * stride_s, raw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          float q;
           if (all_exact) {  // shared-divisor division, see SharedDivisor
             const float q0 = __fmul_rn(raw[i], rc[i]);
-            q = __fmaf_rn(__fmaf_rn(-sc[i], q0, raw[i]), rc[i], q0);
+            q[j][i] = __fmaf_rn(__fmaf_rn(-sc[i], q0, raw[i]), rc[i], q0);
           } else {
-            q = __fdiv_rn(raw[i], sc[i]);
+            q[j][i] = __fdiv_rn(raw[i], sc[i]);
           }
-          q = fminf(fmaxf(q, -v_bound), v_bound);
-          const uint32_t code = __nv_cvt_float_to_fp8(q, __NV_SATFINITE, __NV_E4M3);
-          word[i] |= (code & 0xffu) << (8 * j);
+          // the conversion saturates at +-448 by itself; a tighter bound is applied here
+          if (clamp) q[j][i] = fminf(fmaxf(q[j][i], -v_bound), v_bound);
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[j][i] = 0.f;
       }
+    }
+    uint32_t word[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uint16_t lo, hi;
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(q[1][i]), "f"(q[0][i]));
+      asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(q[3][i]), "f"(q[2][i]));
+      word[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
@@ -327,15 +344,16 @@ static int launch_quant_qk(const void *x, int64_t sh, int64_t ss, const float *m
   const int blocks = ceil_div(rows, block);
   const int blocks_total = ceil_div(sequence_total, block);
   dim3 grid(blocks, heads);
+#define H3S_LAUNCH_QK(BLOCK, HAS_MEAN)                                                               \
+  quant_qk_blocks_kernel<T, BLOCK, HAS_MEAN><<<grid, BLOCK * 2, 0, stream>>>(                         \
+      static_cast<const T *>(x), sh, ss, mean, out, scale, summary, summary_dtype, rows, row_start, \
+      sequence_total, blocks_total)
   if (block == H3S_Q_TILE) {
-    quant_qk_blocks_kernel<T, H3S_Q_TILE><<<grid, H3S_Q_TILE * 2, 0, stream>>>(
-        static_cast<const T *>(x), sh, ss, mean, out, scale, summary, summary_dtype, rows, row_start,
-        sequence_total, blocks_total);
+    if (mean != nullptr) H3S_LAUNCH_QK(H3S_Q_TILE, true); else H3S_LAUNCH_QK(H3S_Q_TILE, false);
   } else {
-    quant_qk_blocks_kernel<T, H3S_KV_TILE><<<grid, H3S_KV_TILE * 2, 0, stream>>>(
-        static_cast<const T *>(x), sh, ss, mean, out, scale, summary, summary_dtype, rows, row_start,
-        sequence_total, blocks_total);
+    if (mean != nullptr) H3S_LAUNCH_QK(H3S_KV_TILE, true); else H3S_LAUNCH_QK(H3S_KV_TILE, false);
   }
+#undef H3S_LAUNCH_QK
   H3S_CHECK_CUDA(cudaGetLastError());
   return H3S_OK;
 }
