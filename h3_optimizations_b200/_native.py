@@ -50,6 +50,9 @@ PROTOTYPES = {
     "h3s_convrot_quant_rows": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "h3s_qkv_gemm_chunk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                    c_int64, c_void_p, c_void_p]),
+    "h3s_qkv_gemm_chunk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p]),
     "h3s_route_topk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_void_p]),
     "h3s_route_to_delta_lut": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,

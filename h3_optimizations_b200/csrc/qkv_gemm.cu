@@ -118,7 +118,76 @@ struct GemmParams {
   int32_t *status;
   int rows, n_out, hidden;
   int m_tiles, n_tiles;
+  // optional per-head RMS norm (+ split-half rotation) of the Q and K groups
+  const float *q_norm;    // (128) or null: no norm, no rotation
+  const float *k_norm;    // (128)
+  const void *rope;       // (rows, 48, 2, 2) view with the strides below, or null
+  int64_t rope_stride_seq, rope_stride_dim, rope_stride_rot, rope_stride_pair;
+  int rope_dtype;         // H3S_F32 or H3S_BF16
+  int heads;
+  float epsilon;
 };
+
+__device__ __forceinline__ float rope_load(const void *base, int64_t index, int dtype) {
+  return dtype == H3S_F32 ? __ldg(static_cast<const float *>(base) + index)
+                          : __bfloat162float(__ldg(static_cast<const __nv_bfloat16 *>(base) + index));
+}
+
+__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&t);
+}
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// One row of one Q or K head after the GEMM, held as 64 bf16 pairs (every
+// intermediate of the reference epilogue is rounded to bf16, so the packed
+// form loses nothing): RMS norm over the 128 channels with the per-channel
+// weight, then the split-half rotation of channels [0,48) against [48,96).
+// Same order of operations and roundings as the reference
+// (attention/sparse/fused_qkv.py:218-289); the sum of squares is accumulated
+// in FP64 so that it does not depend on the order of the additions.
+__device__ __forceinline__ void norm_rope_row(uint32_t (&y)[H3S_HEAD_DIM / 2], const float *__restrict__ norm_weight,
+                                              float epsilon, const void *rope_row, int rope_dtype,
+                                              int64_t stride_dim, int64_t stride_rot, int64_t stride_pair) {
+  double sum = 0.0;
+#pragma unroll
+  for (int i = 0; i < H3S_HEAD_DIM / 2; ++i) {
+    const double lo = static_cast<double>(bf16_lo(y[i])), hi = static_cast<double>(bf16_hi(y[i]));
+    sum = fma(lo, lo, sum);
+    sum = fma(hi, hi, sum);
+  }
+  const float mean = __fadd_rn(__fmul_rn(static_cast<float>(sum), 1.0f / H3S_HEAD_DIM), epsilon);
+  const float inverse_rms = __frsqrt_rn(mean);
+#pragma unroll
+  for (int i = 0; i < H3S_HEAD_DIM / 2; ++i) {
+    const float2 w = __ldg(reinterpret_cast<const float2 *>(norm_weight) + i);
+    y[i] = pack_bf16x2(__fmul_rn(__fmul_rn(bf16_lo(y[i]), inverse_rms), w.x),
+                       __fmul_rn(__fmul_rn(bf16_hi(y[i]), inverse_rms), w.y));
+  }
+  if (rope_row != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 24; ++i) {  // channels 2i, 2i+1 against 2i+48, 2i+49
+      float first[2] = {bf16_lo(y[i]), bf16_hi(y[i])};
+      float second[2] = {bf16_lo(y[i + 24]), bf16_hi(y[i + 24])};
+      float out_first[2], out_second[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int64_t at = (2 * i + e) * stride_dim;
+        const float f00 = rope_load(rope_row, at, rope_dtype);
+        const float f01 = rope_load(rope_row, at + stride_pair, rope_dtype);
+        const float f10 = rope_load(rope_row, at + stride_rot, rope_dtype);
+        const float f11 = rope_load(rope_row, at + stride_rot + stride_pair, rope_dtype);
+        out_first[e] = __fadd_rn(__fmul_rn(f00, first[e]), __fmul_rn(f01, second[e]));
+        out_second[e] = __fadd_rn(__fmul_rn(f10, first[e]), __fmul_rn(f11, second[e]));
+      }
+      y[i] = pack_bf16x2(out_first[0], out_first[1]);
+      y[i + 24] = pack_bf16x2(out_second[0], out_second[1]);
+    }
+  }
+}
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -215,26 +284,65 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const bool row_ok = row < prm.rows;
       const float xs = row_ok ? __ldg(prm.x_scale + row) : 0.f;
 #pragma unroll 1
-      for (int cc = 0; cc < kGemmN / 32; ++cc) {
-        uint32_t acc[32];
-        H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + cc * 32, acc);
-        ptx::tmem_wait_ld();
-        const int col0 = tn * kGemmN + cc * 32;
-        if (row_ok && col0 < prm.n_out) {
-          const int group = col0 >> 7;  // 128-column group == (kind, head)
-          __nv_bfloat16 *dst = prm.out + group * prm.out_stride_head + static_cast<int64_t>(row) * H3S_HEAD_DIM + (col0 & 127);
+      for (int gi = 0; gi < kGemmN / H3S_HEAD_DIM; ++gi) {
+        const int group_col0 = tn * kGemmN + gi * H3S_HEAD_DIM;
+        const int group = group_col0 >> 7;  // 128-column group == (kind, head)
+        const bool group_ok = group_col0 < prm.n_out;
+        const bool normed = prm.q_norm != nullptr && group < 2 * prm.heads;
+        if (!normed) {
+#pragma unroll 1
+          for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+            uint32_t acc[32];
+            H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + gi * H3S_HEAD_DIM + cc * 32, acc);
+            ptx::tmem_wait_ld();
+            const int col0 = group_col0 + cc * 32;
+            if (row_ok && group_ok) {
+              __nv_bfloat16 *dst = prm.out + group * prm.out_stride_head + static_cast<int64_t>(row) * H3S_HEAD_DIM + cc * 32;
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint4 w;
-            uint32_t *wp = reinterpret_cast<uint32_t *>(&w);
+              for (int i = 0; i < 32; i += 8) {
+                uint4 w;
+                uint32_t *wp = reinterpret_cast<uint32_t *>(&w);
 #pragma unroll
-            for (int e = 0; e < 8; e += 2) {
-              const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e])), xs), __ldg(prm.w_scale + col0 + i + e));
-              const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e + 1])), xs), __ldg(prm.w_scale + col0 + i + e + 1));
-              const __nv_bfloat162 t = __floats2bfloat162_rn(y0, y1);
-              wp[e >> 1] = *reinterpret_cast<const uint32_t *>(&t);
+                for (int e = 0; e < 8; e += 2) {
+                  const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e])), xs), __ldg(prm.w_scale + col0 + i + e));
+                  const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e + 1])), xs), __ldg(prm.w_scale + col0 + i + e + 1));
+                  const __nv_bfloat162 t = __floats2bfloat162_rn(y0, y1);
+                  wp[e >> 1] = *reinterpret_cast<const uint32_t *>(&t);
+                }
+                *reinterpret_cast<uint4 *>(dst + i) = w;
+              }
             }
-            *reinterpret_cast<uint4 *>(dst + i) = w;
+          }
+        } else {
+          // Q or K head: the whole 128-channel row of this thread is needed at once
+          uint32_t y[H3S_HEAD_DIM / 2];
+#pragma unroll
+          for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+            uint32_t acc[32];
+            H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + gi * H3S_HEAD_DIM + cc * 32, acc);
+            ptx::tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float2 ws = __ldg(reinterpret_cast<const float2 *>(prm.w_scale + group_col0 + cc * 32 + i));
+              y[cc * 16 + (i >> 1)] =
+                  pack_bf16x2(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i])), xs), ws.x),
+                              __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + 1])), xs), ws.y));
+            }
+          }
+          if (row_ok && group_ok) {
+            const void *rope_row = nullptr;
+            if (prm.rope != nullptr) {
+              const int64_t offset = static_cast<int64_t>(row) * prm.rope_stride_seq;
+              rope_row = prm.rope_dtype == H3S_F32
+                             ? static_cast<const void *>(static_cast<const float *>(prm.rope) + offset)
+                             : static_cast<const void *>(static_cast<const __nv_bfloat16 *>(prm.rope) + offset);
+            }
+            norm_rope_row(y, group < prm.heads ? prm.q_norm : prm.k_norm, prm.epsilon, rope_row, prm.rope_dtype,
+                          prm.rope_stride_dim, prm.rope_stride_rot, prm.rope_stride_pair);
+            __nv_bfloat16 *dst = prm.out + group * prm.out_stride_head + static_cast<int64_t>(row) * H3S_HEAD_DIM;
+#pragma unroll
+            for (int i = 0; i < H3S_HEAD_DIM / 2; i += 4)
+              *reinterpret_cast<uint4 *>(dst + 2 * i) = make_uint4(y[i], y[i + 1], y[i + 2], y[i + 3]);
           }
         }
       }
@@ -295,20 +403,31 @@ int h3s_convrot_quant_rows(const void *x, int64_t x_stride_row, int rows, int hi
   return H3S_OK;
 }
 
-int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8, const float *w_scale,
-                       int rows, int hidden, int n_out, void *out_bf16, int64_t out_stride_head,
-                       int32_t *status, h3s_stream_t stream) {
+static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8, const float *w_scale,
+                               int rows, int hidden, int n_out, void *out_bf16, int64_t out_stride_head,
+                               const float *q_norm, const float *k_norm, float epsilon, const void *rope,
+                               int rope_dtype, const int64_t *rope_strides, int heads, int32_t *status,
+                               h3s_stream_t stream, const char *who) {
   using namespace h3s;
-  H3S_CHECK_ARG(x_i8 && x_scale && w_i8 && w_scale && out_bf16, "qkv_gemm_chunk: NULL pointer");
-  H3S_CHECK_ARG(rows > 0 && hidden > 0 && hidden % kGemmK == 0, "qkv_gemm_chunk: hidden %d must be a positive multiple of 128", hidden);
-  H3S_CHECK_ARG(n_out > 0 && n_out % H3S_HEAD_DIM == 0, "qkv_gemm_chunk: n_out %d must be a multiple of 128", n_out);
+  H3S_CHECK_ARG(x_i8 && x_scale && w_i8 && w_scale && out_bf16, "%s: NULL pointer", who);
+  H3S_CHECK_ARG(rows > 0 && hidden > 0 && hidden % kGemmK == 0, "%s: hidden %d must be a positive multiple of 128", who, hidden);
+  H3S_CHECK_ARG(n_out > 0 && n_out % H3S_HEAD_DIM == 0, "%s: n_out %d must be a multiple of 128", who, n_out);
   H3S_CHECK_ARG(out_stride_head >= static_cast<int64_t>(rows) * H3S_HEAD_DIM && out_stride_head % 8 == 0,
-                "qkv_gemm_chunk: out_stride_head %lld is smaller than rows*128", static_cast<long long>(out_stride_head));
+                "%s: out_stride_head %lld is smaller than rows*128", who, static_cast<long long>(out_stride_head));
   H3S_CHECK_ARG(((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
-                "qkv_gemm_chunk: operands must be 16-byte aligned");
+                "%s: operands must be 16-byte aligned", who);
+  if (q_norm != nullptr || k_norm != nullptr || rope != nullptr) {
+    H3S_CHECK_ARG(q_norm != nullptr && k_norm != nullptr, "%s: both norm weights are needed", who);
+    H3S_CHECK_ARG(heads > 0 && n_out == 3 * heads * H3S_HEAD_DIM, "%s: n_out %d is not 3*heads*128 for %d heads", who, n_out, heads);
+    H3S_CHECK_ARG(epsilon >= 0.f, "%s: negative epsilon", who);
+    if (rope != nullptr) {
+      H3S_CHECK_ARG(rope_strides != nullptr, "%s: rope strides missing", who);
+      H3S_CHECK_ARG(rope_dtype == H3S_F32 || rope_dtype == H3S_BF16, "%s: rope must be fp32 or bf16", who);
+    }
+  }
   const int cap = h3s_device_capability();
   if (cap < 0) return cap;
-  if (cap / 10 != 10) return fail(H3S_EARCH, "qkv_gemm_chunk: needs an sm_100 device, found sm_%d", cap);
+  if (cap / 10 != 10) return fail(H3S_EARCH, "%s: needs an sm_100 device, found sm_%d", who, cap);
   CUtensorMap ma, mb;
   int rc = make_tensor_map_u8_2d(&ma, x_i8, hidden, rows, hidden, kGemmK, kGemmM, "qkv_gemm_chunk A map");
   if (rc) return rc;
@@ -319,6 +438,10 @@ int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale, const int8_t *w
   prm.out_stride_head = out_stride_head; prm.status = status;
   prm.rows = rows; prm.n_out = n_out; prm.hidden = hidden;
   prm.m_tiles = ceil_div(rows, kGemmM); prm.n_tiles = ceil_div(n_out, kGemmN);
+  prm.q_norm = q_norm; prm.k_norm = k_norm; prm.rope = rope; prm.rope_dtype = rope_dtype;
+  prm.rope_stride_seq = rope ? rope_strides[0] : 0; prm.rope_stride_dim = rope ? rope_strides[1] : 0;
+  prm.rope_stride_rot = rope ? rope_strides[2] : 0; prm.rope_stride_pair = rope ? rope_strides[3] : 0;
+  prm.heads = heads; prm.epsilon = epsilon;
   int device = 0, sms = 0;
   H3S_CHECK_CUDA(cudaGetDevice(&device));
   H3S_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
@@ -329,6 +452,24 @@ int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale, const int8_t *w
   qkv_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
   H3S_CHECK_CUDA(cudaGetLastError());
   return H3S_OK;
+}
+
+int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8, const float *w_scale,
+                       int rows, int hidden, int n_out, void *out_bf16, int64_t out_stride_head,
+                       int32_t *status, h3s_stream_t stream) {
+  return qkv_gemm_chunk_impl(x_i8, x_scale, w_i8, w_scale, rows, hidden, n_out, out_bf16, out_stride_head, nullptr,
+                             nullptr, 0.f, nullptr, H3S_F32, nullptr, 0, status, stream, "qkv_gemm_chunk");
+}
+
+int h3s_qkv_gemm_chunk_norm_rope(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8,
+                                 const float *w_scale, int rows, int hidden, int heads, void *out_bf16,
+                                 int64_t out_stride_head, const float *q_norm, const float *k_norm,
+                                 float epsilon, const void *rope, int rope_dtype, const int64_t *rope_strides,
+                                 int32_t *status, h3s_stream_t stream) {
+  H3S_CHECK_ARG(q_norm != nullptr && k_norm != nullptr, "qkv_gemm_chunk_norm_rope: NULL norm weight");
+  return qkv_gemm_chunk_impl(x_i8, x_scale, w_i8, w_scale, rows, hidden, 3 * heads * H3S_HEAD_DIM, out_bf16,
+                             out_stride_head, q_norm, k_norm, epsilon, rope, rope_dtype, rope_strides, heads, status,
+                             stream, "qkv_gemm_chunk_norm_rope");
 }
 
 }  // extern "C"

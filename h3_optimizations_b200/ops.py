@@ -204,9 +204,15 @@ def convrot_quant_rows(x, x_i8=None, x_scale=None):
     return x_i8[:rows], x_scale[:rows]
 
 
-def qkv_gemm_chunk(x_i8, x_scale, w_i8, w_scale, staging, *, row_start=0, status=None):
+def qkv_gemm_chunk(x_i8, x_scale, w_i8, w_scale, staging, *, row_start=0, status=None,
+                   q_norm=None, k_norm=None, epsilon=1e-6, rope=None):
     """INT8 GEMM of one chunk into ``staging`` bf16 ``(groups, S, 128)`` (group =
-    kind*H + head) at rows ``[row_start, row_start + rows)``."""
+    kind*H + head) at rows ``[row_start, row_start + rows)``.
+
+    With ``q_norm`` / ``k_norm`` (fp32 ``(128,)`` weights) the Q and K heads get
+    the per-head RMS norm in the epilogue, and with ``rope`` (the model's
+    ``(1, S, 1, 48, 2, 2)`` tensor, fp32 or bf16, whole sequence) also the
+    split-half rotation of the chunk's rows."""
     lib = _native.load()
     rows, hidden = x_i8.shape
     n_out = w_i8.shape[0]
@@ -219,10 +225,36 @@ def qkv_gemm_chunk(x_i8, x_scale, w_i8, w_scale, staging, *, row_start=0, status
     if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 or x_scale.numel() < rows or w_scale.numel() != n_out:
         raise _native.NativeError("qkv_gemm_chunk: scales must be fp32 (rows,) and (n_out,)")
     base = ctypes.c_void_p(staging.data_ptr() + int(row_start) * HEAD_DIM * staging.element_size())
+    if q_norm is None and k_norm is None and rope is None:
+        check(
+            lib.h3s_qkv_gemm_chunk(ptr(x_i8), ptr(x_scale), ptr(w_i8), ptr(w_scale), rows, hidden, n_out, base,
+                                   staging.stride(0), ptr(status), stream_ptr(x_i8.device)),
+            "h3s_qkv_gemm_chunk",
+        )
+        return
+    if q_norm is None or k_norm is None:
+        raise _native.NativeError("qkv_gemm_chunk: q_norm and k_norm go together (RoPE needs both)")
+    if n_out % (3 * HEAD_DIM):
+        raise _native.NativeError("qkv_gemm_chunk: n_out %d is not 3*heads*128" % n_out)
+    for name, weight in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if weight.dtype != torch.float32 or tuple(weight.shape) != (HEAD_DIM,) or not weight.is_contiguous() \
+                or weight.device != x_i8.device:
+            raise _native.NativeError("qkv_gemm_chunk: %s must be a contiguous fp32 (128,) tensor on the GEMM's device" % name)
+    rope_ptr, rope_code, strides = None, 0, None
+    if rope is not None:
+        sequence = staging.shape[1]
+        if (rope.ndim != 6 or tuple(rope.shape[:3]) != (1, sequence, 1) or tuple(rope.shape[3:]) != (48, 2, 2)
+                or rope.device != x_i8.device or rope.dtype not in (torch.float32, torch.bfloat16)):
+            raise _native.NativeError("qkv_gemm_chunk: rope must be fp32/bf16 (1, %d, 1, 48, 2, 2) on the GEMM's device" % sequence)
+        rope_ptr = ctypes.c_void_p(rope.data_ptr() + int(row_start) * rope.stride(1) * rope.element_size())
+        rope_code = dtype_code(rope.dtype)
+        strides = (ctypes.c_int64 * 4)(rope.stride(1), rope.stride(3), rope.stride(4), rope.stride(5))
     check(
-        lib.h3s_qkv_gemm_chunk(ptr(x_i8), ptr(x_scale), ptr(w_i8), ptr(w_scale), rows, hidden, n_out, base,
-                               staging.stride(0), ptr(status), stream_ptr(x_i8.device)),
-        "h3s_qkv_gemm_chunk",
+        lib.h3s_qkv_gemm_chunk_norm_rope(
+            ptr(x_i8), ptr(x_scale), ptr(w_i8), ptr(w_scale), rows, hidden, n_out // (3 * HEAD_DIM), base,
+            staging.stride(0), ptr(q_norm), ptr(k_norm), float(epsilon), rope_ptr, rope_code, strides, ptr(status),
+            stream_ptr(x_i8.device)),
+        "h3s_qkv_gemm_chunk_norm_rope",
     )
 
 

@@ -18,10 +18,12 @@ chunked_qkv.py:289) K is quantised per chunk as well.
 The module handed to ``project`` must expose ``heads``, ``head_dim`` and the
 INT8 weight in the rotated domain: ``qkv_weight_int8`` (3*H*128, hidden) with
 rows ordered ``[Q heads | K heads | V heads]`` (fused_qkv.py:195,394) and
-``qkv_weight_scale`` (3*H*128,) fp32.  Per-head RMSNorm and RoPE are not part
-of this provider yet: ``try_project`` declines (returns None) when
-``rope_freqs`` is given, which makes the forward boundary fall back to its own
-projection (attention_forward.py:78-96,161-177).
+``qkv_weight_scale`` (3*H*128,) fp32.  When the module carries ``q_norm`` and
+``k_norm`` (objects with ``weight`` (128,) and ``eps``) the per-head RMS norm of
+Q and K runs in the GEMM epilogue, and with ``rope_freqs`` (1,S,1,48,2,2) the
+split-half rotation as well (fused_qkv.py:225-289); a module without norms
+(the benchmark configuration) is projected without either, and asking for the
+rotation without norms is an error.
 """
 
 from __future__ import annotations
@@ -70,7 +72,7 @@ class ChunkedSparseQKVProjector:
     # -- protocol ---------------------------------------------------------
 
     def try_project(self, module, x, rope_freqs, *, layer_index, transformer_options):
-        if rope_freqs is not None:
+        if rope_freqs is not None and (getattr(module, "q_norm", None) is None or getattr(module, "k_norm", None) is None):
             return None
         if getattr(module, "qkv_weight_int8", None) is None or getattr(module, "qkv_weight_scale", None) is None:
             return None
@@ -78,22 +80,30 @@ class ChunkedSparseQKVProjector:
 
     def project(self, module, x, rope_freqs, *, layer_index, transformer_options):
         del transformer_options
-        if rope_freqs is not None:
-            raise FusedQKVError("the B200 chunked QKV provider does not apply RoPE; project without rope_freqs")
         weight = getattr(module, "qkv_weight_int8", None)
         scale = getattr(module, "qkv_weight_scale", None)
         if weight is None or scale is None:
             raise FusedQKVError("module does not expose qkv_weight_int8 / qkv_weight_scale")
+        q_norm, k_norm = getattr(module, "q_norm", None), getattr(module, "k_norm", None)
+        if (q_norm is None) != (k_norm is None):
+            raise FusedQKVError("module must carry both q_norm and k_norm or neither")
+        if rope_freqs is not None and q_norm is None:
+            raise FusedQKVError("RoPE in the QKV epilogue needs the module's q_norm / k_norm")
+        norm = None
+        if q_norm is not None:
+            if float(q_norm.eps) != float(k_norm.eps):
+                raise FusedQKVError("q_norm and k_norm use different epsilons")
+            norm = (q_norm.weight, k_norm.weight, float(q_norm.eps))
         return run_chunked_sparse_qkv(
             x, weight, scale, heads=int(module.heads), head_dim=int(module.head_dim),
             layer_index=layer_index, chunk_rows=self.chunk_rows, smooth_k=self.smooth_k,
-            summary_dtype=self.summary_dtype,
+            summary_dtype=self.summary_dtype, norm=norm, rope_freqs=rope_freqs,
         )
 
 
 def run_chunked_sparse_qkv(x, w_i8, w_scale, *, heads, head_dim=HEAD_DIM, layer_index=0,
                            chunk_rows=CHUNK_ROWS, smooth_k=True, summary_dtype=torch.float32,
-                           status=None):
+                           status=None, norm=None, rope_freqs=None):
     if not x.is_cuda or x.dtype != torch.bfloat16 or x.ndim != 2:
         raise FusedQKVError("chunked Sparse Sage QKV requires a rank-2 CUDA BF16 input")
     if torch.is_grad_enabled() and x.requires_grad:
@@ -108,6 +118,22 @@ def run_chunked_sparse_qkv(x, w_i8, w_scale, *, heads, head_dim=HEAD_DIM, layer_
     if tuple(w_scale.shape) != (n_out,) or w_scale.dtype != torch.float32:
         raise FusedQKVError("QKV weight scale must be fp32 (%d,)" % n_out)
     device = x.device
+    q_norm = k_norm = None
+    epsilon = 0.0
+    if norm is not None:
+        q_norm, k_norm, epsilon = norm
+        q_norm = q_norm.detach().to(device=device, dtype=torch.float32).contiguous()
+        k_norm = k_norm.detach().to(device=device, dtype=torch.float32).contiguous()
+        if tuple(q_norm.shape) != (HEAD_DIM,) or tuple(k_norm.shape) != (HEAD_DIM,):
+            raise FusedQKVError("q_norm / k_norm weights must have 128 elements")
+    if rope_freqs is not None:
+        if norm is None:
+            raise FusedQKVError("RoPE in the QKV epilogue needs the q_norm / k_norm weights")
+        if (rope_freqs.ndim != 6 or tuple(rope_freqs.shape[:3]) != (1, sequence, 1)
+                or tuple(rope_freqs.shape[3:]) != (48, 2, 2) or rope_freqs.device != device):
+            raise FusedQKVError("rope_freqs must be (1, %d, 1, 48, 2, 2) on the projection's device" % sequence)
+        if rope_freqs.dtype not in (torch.float32, torch.bfloat16):
+            rope_freqs = rope_freqs.float()
     try:
         q_blocks = (sequence + Q_TILE - 1) // Q_TILE
         k_blocks = (sequence + KV_TILE - 1) // KV_TILE
@@ -130,7 +156,8 @@ def run_chunked_sparse_qkv(x, w_i8, w_scale, *, heads, head_dim=HEAD_DIM, layer_
         for start, end in chunk_ranges(sequence, chunk_rows):
             rows = end - start
             ops.convrot_quant_rows(x[start:end], x_i8, x_scale)
-            ops.qkv_gemm_chunk(x_i8[:rows], x_scale[:rows], w_i8, w_scale, staging, row_start=start, status=status)
+            ops.qkv_gemm_chunk(x_i8[:rows], x_scale[:rows], w_i8, w_scale, staging, row_start=start, status=status,
+                               q_norm=q_norm, k_norm=k_norm, epsilon=epsilon, rope=rope_freqs)
             ops.quant_qk_blocks_into(q_stage[:, :, start:end], q_int8, q_scale, q_summary, block=Q_TILE, row_start=start)
             if not smooth_k:
                 ops.quant_qk_blocks_into(k_stage[:, :, start:end], k_int8, k_scale, k_summary, block=KV_TILE, row_start=start)

@@ -177,6 +177,29 @@ int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale,
                        int64_t out_stride_head, int32_t *status,
                        h3s_stream_t stream);
 
+/*
+ * The same GEMM with the per-head RMS norm and the split-half rotary embedding
+ * of the Q and K heads applied in its epilogue (V heads pass through):
+ *   y    = bf16(acc * x_scale[row] * w_scale[col])
+ *   y    = bf16(y * rsqrt(mean_d(y^2) + epsilon) * norm[d])       norm = q_norm | k_norm, fp32 (128)
+ *   y[d], y[d+48] = bf16(f00*y[d] + f01*y[d+48]), bf16(f10*y[d] + f11*y[d+48])   for d < 48
+ * with f(a,b) = rope[row*rope_strides[0] + d*rope_strides[1] + a*rope_strides[2]
+ * + b*rope_strides[3]] (element strides; rope_dtype H3S_F32 or H3S_BF16), i.e.
+ * the (1,S,1,48,2,2) tensor of the model offset to the chunk's first row.
+ * rope == NULL: norm only.  n_out = 3*heads*128.
+ * Replaces the norm/rotation part of _fused_qk_kernel
+ * (attention/sparse/fused_qkv.py:225-289) and rms_rope_split_half_ as used in
+ * attention_forward.py:10-48.
+ */
+int h3s_qkv_gemm_chunk_norm_rope(const int8_t *x_i8, const float *x_scale,
+                                 const int8_t *w_i8, const float *w_scale,
+                                 int rows, int hidden, int heads,
+                                 void *out_bf16, int64_t out_stride_head,
+                                 const float *q_norm, const float *k_norm,
+                                 float epsilon, const void *rope,
+                                 int rope_dtype, const int64_t *rope_strides,
+                                 int32_t *status, h3s_stream_t stream);
+
 /* Router ---------------------------------------------------------------- */
 
 /*

@@ -492,6 +492,46 @@ def qkv_project_int8(x_i8, x_scale, w_i8, w_scale, out_dtype=torch.bfloat16):
     return y.to(out_dtype)
 
 
+def rms_norm_rope_split_half(y, heads, q_norm, k_norm, epsilon, rope=None, head_dim=HEAD_DIM):
+    """Per-head RMS norm and split-half rotation of the Q and K columns of a
+    projected ``(S, 3*H*D)`` bf16 tensor; V columns pass through.  Follows the
+    fused epilogue of the reference (attention/sparse/fused_qkv.py:225-289):
+
+        v = bf16(y * rsqrt(sum_d y^2 / D + eps) * w[d])
+        v[d], v[d+48] = bf16(f00*v[d] + f01*v[d+48]), bf16(f10*v[d] + f11*v[d+48])   d < 48
+
+    with ``f = rope[0, s, 0, d]`` (2x2), every product and sum rounded to FP32.
+    The sum of squares is taken in FP64 and rounded once, and the reciprocal
+    square root is the correctly rounded one: the Triton kernel's reduction
+    order and its approximate ``rsqrt`` are not pinned by any reference test
+    (parity unpinned), so the restatement picks the order-free definition."""
+    rows = y.shape[0]
+    t = y.to(torch.bfloat16).float().reshape(rows, 3, heads, head_dim).clone()
+    for kind, weight in ((0, q_norm), (1, k_norm)):
+        x = t[:, kind]
+        ss = (x.double() * x.double()).sum(dim=-1, keepdim=True).float()
+        mean = ss * (1.0 / head_dim) + torch.tensor(float(epsilon), dtype=torch.float32)
+        inverse_rms = (1.0 / mean.double().sqrt()).float()
+        x = ((x * inverse_rms) * weight.float()).to(torch.bfloat16).float()
+        if rope is not None:
+            pairs = rope.shape[-3]
+            f = rope.reshape(rows, 1, pairs, 2, 2).float()
+            first, second = x[..., :pairs], x[..., pairs:2 * pairs]
+            rotated_first = f[..., 0, 0] * first + f[..., 0, 1] * second
+            rotated_second = f[..., 1, 0] * first + f[..., 1, 1] * second
+            x = torch.cat([rotated_first, rotated_second, x[..., 2 * pairs:]], dim=-1).to(torch.bfloat16).float()
+        t[:, kind] = x
+    return t.reshape(rows, 3 * heads * head_dim).to(torch.bfloat16)
+
+
+def make_rope(sequence):
+    """The rotary table the reference's benchmarks use
+    (benchmarks/bench_chunked_kitchen_qkv.py:193-204): bf16 (1,S,1,48,2,2)."""
+    angles = torch.arange(sequence * 48, dtype=torch.float32).reshape(sequence, 48) * (1.0 / 8192.0)
+    c, s = torch.cos(angles), torch.sin(angles)
+    return torch.stack((c, -s, s, c), dim=-1).reshape(1, sequence, 1, 48, 2, 2).to(torch.bfloat16)
+
+
 def split_heads_hnd(y, heads, head_dim=HEAD_DIM):
     """Columns ordered ``[Q heads | K heads | V heads]``, row
     ``kind*H*D + head*D + d`` (fused_qkv.py:195,394) -> three ``(1,H,S,D)``."""
