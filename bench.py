@@ -100,8 +100,46 @@ class ClockSampler:
         self.index = index
         self.proc = None
         self.file = None
+        self.thread = None
+        self.samples = []
+        self.stop_flag = False
+
+    # NVML (read-only queries) from a thread every ~2 ms when the bindings are
+    # there - a timed region of a few tens of milliseconds still gets samples -
+    # else nvidia-smi every 100 ms.
+    def _nvml_loop(self, nvml, handle):
+        reasons_fn = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        bits = {
+            "hw_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self.stop_flag:
+            try:
+                sm = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
+                power = nvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
+                mask = reasons_fn(handle)
+                self.samples.append((float(sm), power, [n for n, bit in bits.items() if mask & bit]))
+            except Exception:
+                break
+            time.sleep(0.002)
 
     def start(self):
+        try:
+            import pynvml as nvml
+
+            nvml.nvmlInit()
+            handle = nvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.sm_max = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            import threading
+
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
@@ -111,6 +149,15 @@ class ClockSampler:
             self.proc = None
 
     def stop(self):
+        if self.thread is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            if not self.samples:
+                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no NVML samples"}
+            reasons = sorted({r for _, _, rs in self.samples for r in rs})
+            return {"sm_mhz": statistics.median(s for s, _, _ in self.samples), "sm_max_mhz": self.sm_max,
+                    "power_w_max": max(p for _, p, _ in self.samples), "samples": len(self.samples),
+                    "reasons": reasons, "source": "NVML queries every 2 ms during the timed region"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "nvidia-smi unavailable"}
         time.sleep(0.15)
@@ -139,7 +186,7 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no samples"}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi -lms 100"}
 
 
 def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4):
@@ -257,6 +304,22 @@ def run_config2(args, spec):
     for _ in range(args.steps): gemm_all()
     g1.record(); torch.cuda.synchronize()
     gemm_ms = g0.elapsed_time(g1) / args.steps
+    # the same GEMM with the per-head RMS norm and split-half rotation in its epilogue
+    gen = torch.Generator().manual_seed(1)
+    q_norm = (torch.rand(HEAD_DIM, generator=gen) + 0.5).to(device)
+    k_norm = (torch.rand(HEAD_DIM, generator=gen) + 0.5).to(device)
+    angles = torch.arange(spec.sequence * 48, dtype=torch.float32).reshape(spec.sequence, 48) * (1.0 / 8192.0)
+    rope = torch.stack((torch.cos(angles), -torch.sin(angles), torch.sin(angles), torch.cos(angles)), dim=-1)
+    rope = rope.reshape(1, spec.sequence, 1, 48, 2, 2).to(torch.bfloat16).to(device)
+    def gemm_norm_rope_all():
+        for a, b in chunks:
+            ops.qkv_gemm_chunk(x_i8[a:b], x_scale[a:b], w, w_scale, staging, row_start=a, q_norm=q_norm,
+                               k_norm=k_norm, epsilon=1e-6, rope=rope)
+    for _ in range(3): gemm_norm_rope_all()
+    n0, n1 = events(); n0.record()
+    for _ in range(args.steps): gemm_norm_rope_all()
+    n1.record(); torch.cuda.synchronize()
+    gemm_norm_rope_ms = n0.elapsed_time(n1) / args.steps
     c0, c1 = events(); c0.record()
     for _ in range(args.steps): ops.convrot_quant_rows(x, x_i8, x_scale)
     c1.record(); torch.cuda.synchronize()
@@ -278,7 +341,8 @@ def run_config2(args, spec):
                    "algorithmic_ops": {"attention": attn_ops, "qkv_gemm": gemm_ops},
                    "l2_policy": "activations + staging (>800 MB) exceed the 126 MB L2; no flush"},
         "stages_ms": {"projection (rotate+gemm+carriers)": proj_ms, "router": route_ms, "attention": attn_ms,
-                      "qkv_gemm alone": gemm_ms, "convrot alone": rot_ms},
+                      "qkv_gemm alone": gemm_ms, "qkv_gemm with RMS norm + RoPE epilogue": gemm_norm_rope_ms,
+                      "convrot alone": rot_ms},
         "roofline": {"bound": "tensor", "kernel": "qkv_gemm_kernel", "achieved": gemm_tops, "peak": int8_peak,
                      "unit": "TOP/s", "frac": gemm_tops / int8_peak, "frac_of_nominal_4500": gemm_tops / NOMINAL_INT8_TOPS,
                      "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s)" % peak_source, "traffic": None},

@@ -176,6 +176,13 @@ class B200SparseBackend:
             raise SparseSageError("Sparse Sage requires CUDA")
         return heads, sequence
 
+    def _side_stream(self, device):
+        streams = self.__dict__.setdefault("_side_streams", {})
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        if key not in streams:
+            streams[key] = torch.cuda.Stream(device)
+        return streams[key]
+
     # -- protocol -------------------------------------------------------------
 
     def prepare(self, q, k, v, *, layer_index, transformer_options):
@@ -190,9 +197,18 @@ class B200SparseBackend:
             need_route = retained < geometry.pure_video_kv_tiles
             summary_dtype = torch.float64 if need_route else None
             k_mean, v_scale = ops.column_stats(k if self.smooth_k else None, v, V_QUANT_BOUND)
+            # The V carrier depends on nothing but the statistics, and the router
+            # (latency bound, a tenth of the SMs' issue slots) leaves the GPU mostly
+            # idle: V is quantised on a second stream underneath the Q/K quantisers
+            # and the router, and joins before the carriers are handed out.
+            main = torch.cuda.current_stream(q.device)
+            side = self._side_stream(q.device)
+            v_carrier = ops.allocate_v_carrier(sequence, heads, v.device)
+            side.wait_stream(main)
+            with torch.cuda.stream(side):
+                ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
             q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
             k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
-            v_carrier, v_scale = ops.quant_v_fp8(v, v_scale, V_QUANT_BOUND)
             if need_route:
                 route = self.router.build_route_from_summaries(
                     q_summary, k_summary, snapshot.layout, video_budget,
@@ -202,6 +218,7 @@ class B200SparseBackend:
                 route = self.router.build_route(
                     q, k, snapshot.layout, video_budget, **self._sink(transformer_options, layer_index)
                 )
+            main.wait_stream(side)
         except SparseRouterError as exc:
             raise SparseSageError("sparse routing failed: %s" % exc) from exc
         except _native.NativeError as exc:

@@ -1,0 +1,101 @@
+"""Size-independent properties of the hot path at the full config-1 and
+config-3 sequence lengths (33272 and 76112 tokens, 4 of the 24 heads), checked
+with independent torch arithmetic on the device rather than with the oracle:
+route shape / order, quantiser scales and round trip, V carrier round trip and
+padding, normalisation of the attention output, determinism."""
+
+import dataclasses
+
+import pytest
+import torch
+
+from h3_optimizations_b200 import workloads
+
+pytestmark = pytest.mark.gpu
+
+HEADS = 4
+
+
+@pytest.fixture(scope="module", params=["config1", "config3"])
+def prepared(request, native_lib):
+    from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, runtime_options
+
+    base = {"config1": workloads.CONFIG1, "config3": workloads.CONFIG3}[request.param]
+    spec = dataclasses.replace(base, heads=HEADS)
+    q, k, v = (t.cuda() for t in workloads.structured_qkv(spec, seed=3))
+    backend = B200SparseBackend(HybridSparseConfig(video_budget=0.3))
+    result = backend.prepare(q, k, v, layer_index=0, transformer_options=runtime_options(spec.layout()))
+    torch.cuda.synchronize()
+    return spec, q, k, v, backend, result
+
+
+def test_route_rows_are_sorted_unique_and_complete(prepared):
+    spec, q, k, v, backend, result = prepared
+    route = result.sparse.route
+    geo, rows = route.geometry, route.indices[0]
+    context = geo.pure_video_kv_start
+    retained = min(geo.pure_video_kv_tiles, max(1, -(-3 * geo.pure_video_kv_tiles // 10)))
+    assert tuple(rows.shape) == (HEADS, geo.pure_video_q_tiles, context + retained)
+    assert bool((rows[..., 1:] > rows[..., :-1]).all()), "every row strictly ascending (sorted, no duplicates)"
+    assert bool((rows[..., :context] == torch.arange(context, device="cuda")).all()), "context tiles come first"
+    assert int(rows.min()) == 0 and int(rows.max()) < geo.kv_tiles
+    assert bool((rows[..., context:] >= context).all())
+
+
+def test_quantiser_scales_and_round_trip(prepared):
+    spec, q, k, v, backend, result = prepared
+    sparse = result.sparse
+    sequence = spec.sequence
+    for x, codes, scale, block in ((q, sparse.q_int8, sparse.q_scale, 128),):
+        blocks = -(-sequence // block)
+        pad = blocks * block - sequence
+        xf = torch.nn.functional.pad(x.float(), (0, 0, 0, pad)).reshape(1, HEADS, blocks, block, 128)
+        expect = xf.abs().amax(dim=(-1, -2)) / 127.0 + 1e-7
+        assert torch.equal(scale, expect), "scale = amax/127 + 1e-7 per block"
+        recon = torch.nn.functional.pad(codes.float(), (0, 0, 0, pad)).reshape(1, HEADS, blocks, block, 128) * scale[..., None, None]
+        steps = (recon - xf).abs() / scale[..., None, None]
+        assert float(steps.max()) <= 0.5 + 1e-3, "round trip within half a quantisation step of the block"
+        assert int(codes.abs().max()) <= 127
+    # K is quantised after removing the per-channel mean over the sequence
+    assert int(sparse.k_int8.abs().max()) <= 127 and tuple(sparse.k_scale.shape) == (1, HEADS, -(-sequence // 64))
+
+
+def test_v_carrier_round_trip_and_padding(prepared):
+    spec, q, k, v, backend, result = prepared
+    sparse = result.sparse
+    sequence = spec.sequence
+    carrier = sparse.v_carrier.float()  # (1, H, 128, padded)
+    assert carrier.shape[-1] % 128 == 0 and carrier.shape[-1] >= sequence
+    assert bool((carrier[..., sequence:] == 0).all()), "padding keys are zero"
+    expect_scale = (v.float().abs().amax(dim=-2) / 448.0).clamp_min(1e-20)
+    assert torch.equal(sparse.v_scale, expect_scale)
+    recon = carrier[..., :sequence].transpose(-1, -2) * sparse.v_scale[..., None, :]
+    err = (recon - v.float()).abs()
+    bound = v.float().abs() * 2.0 ** -4 + sparse.v_scale[..., None, :] * 2.0 ** -9
+    assert bool((err <= bound * 1.001).all()), "E4M3 rounding: 2^-4 relative, 2^-9 of the scale near zero"
+
+
+def test_attention_normalisation_and_determinism(prepared):
+    """With V constant over the sequence (one value per head and channel) the
+    output must be that constant for every query row, whatever the route, tile
+    raggedness or rescaling history: sum(P)/l = 1 up to the FP8 rounding of P
+    (two terms: 2^-7) and of V."""
+    from h3_optimizations_b200 import ops
+
+    spec, q, k, v, backend, result = prepared
+    sparse = result.sparse
+    geo = sparse.route.geometry
+    gen = torch.Generator().manual_seed(7)
+    constant = (torch.rand((1, HEADS, 1, 128), generator=gen) + 0.5).to(torch.bfloat16).cuda()
+    v_const = constant.expand(1, HEADS, spec.sequence, 128).contiguous()
+    carrier, v_scale = ops.quant_v_fp8(v_const)
+    args = (sparse.q_int8, sparse.k_int8, carrier, sparse.q_scale, sparse.k_scale, v_scale, sparse.route.indices)
+    kwargs = dict(q_start=geo.pure_video_q_start, q_stop=geo.pure_video_q_stop, out_dtype=torch.float32)
+    out = ops.sparse_attention(*args, **kwargs)
+    again = ops.sparse_attention(*args, **kwargs)
+    torch.cuda.synchronize()
+    assert torch.equal(out, again), "two launches give identical bits"
+    dequant = carrier[..., :1].float().transpose(-1, -2) * v_scale[..., None, :]  # what the kernel sees as V
+    ratio = out / dequant
+    assert float((ratio - 1.0).abs().max()) < 1.0e-2
+    assert bool(torch.isfinite(out).all())
