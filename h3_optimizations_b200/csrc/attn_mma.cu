@@ -2,7 +2,7 @@
 // (mma.sync m16n8k32, s8 x s8 -> s32 and e4m3 x e4m3 -> f32).
 //
 // Same arithmetic contract as the tcgen05 kernel (integer running maximum,
-// lazy rescale above 2^8, FP32 row sums of the unrounded probabilities), kept
+// lazy rescale above 2^8.75, FP32 row sums of the unrounded probabilities), kept
 // deliberately simple - synchronous tile loads, no pipelining - because its
 // job is to cross-check the tcgen05 kernel on the device at sizes where the
 // CPU checker is too slow.
@@ -180,8 +180,8 @@ sparse_attn_mma_kernel(const int8_t *__restrict__ q8, const int8_t *__restrict__
       imax[h] = max(imax[h], __shfl_xor_sync(0xffffffffu, imax[h], 1));
       imax[h] = max(imax[h], __shfl_xor_sync(0xffffffffu, imax[h], 2));
       const float mx = c * static_cast<float>(imax[h]);
-      if (mx > m_used[h] + 8.0f) {
-        const float m_new = ceilf(mx) - 5.0f;  // largest P in (16,32]; room to 256 before the next rescale
+      if (mx > m_used[h] + 8.75f) {
+        const float m_new = ceilf(mx) - 7.0f;  // largest P in (64,128]; room to 2^8.75 before the next rescale
         const float alpha = ex2(m_used[h] - m_new);
         m_used[h] = m_new;
         l_part[h] *= alpha;

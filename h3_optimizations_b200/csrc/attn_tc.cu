@@ -16,8 +16,8 @@
 // (2 x 256 TMEM columns, 2 x ~98 KB shared memory), so one CTA's softmax
 // overlaps the other's MMAs.
 //
-// O is rescaled lazily: the running maximum is only raised when a tile's
-// maximum exceeds it by more than 8 (P then stays <= 2^8 < 448 = E4M3 max).
+// O is rescaled lazily: the reference point m is only raised when a score
+// exceeds it by more than 8.75 (P then stays <= 2^8.75 = 431 < 448 = E4M3 max).
 #include <climits>
 
 #include "common.cuh"
@@ -38,11 +38,14 @@ constexpr uint32_t kOffV = kOffK + kStages * kKBytes;
 constexpr uint32_t kOffBar = kOffV + kStages * kVBytes;  // P lives in TMEM, not in shared memory
 constexpr uint32_t kAttnSmemBytes = kOffBar + 1024 + 1024;  // barriers/scalars + alignment slack
 // P = exp2(logit - m) with m = ceil(rowmax) - kPOffset when m is (re)set, so the
-// largest probability starts in (16, 32]; m is raised again only when a tile
-// would push P past 2^8 = 256 (E4M3 max 448).  The offset keeps small
-// probabilities and the lo term above the E4M3 underflow threshold (2^-9).
-constexpr float kRescaleThreshold = 8.0f;
-constexpr float kPOffset = 5.0f;
+// largest probability starts in (64, 128]; m is raised again only when a score
+// would push P past 2^8.75 (E4M3 max 448).  FP8 reaches down to 2^-9/2^-10, so
+// keys more than 17-18 bits below the row maximum drop out of the numerator (they
+// stay in the FP32 row sum); with the reference point 5 bits below the maximum
+// instead of 7 a 76k-key row lost up to 6.5 % of its mass that way, now 2.5 %,
+// for ~2 % more time spent rescaling.
+constexpr float kRescaleThreshold = 8.75f;
+constexpr float kPOffset = 7.0f;
 constexpr float kIntBias = 12582912.0f;  // 1.5 * 2^23: float(kIntBias + s) has bits 0x4b400000 + s
 
 enum AbortCode {

@@ -168,20 +168,39 @@ __device__ __forceinline__ void norm_rope_row(uint32_t (&y)[H3S_HEAD_DIM / 2], c
                        __fmul_rn(__fmul_rn(bf16_hi(y[i]), inverse_rms), w.y));
   }
   if (rope_row != nullptr) {
+    // (48,2,2) tables stored contiguously (the layout the model produces) are
+    // read 16 bytes at a time: the eight factors of channels 2i and 2i+1
+    const bool packed = stride_pair == 1 && stride_rot == 2 && stride_dim == 4 &&
+                        (reinterpret_cast<uintptr_t>(rope_row) & 15) == 0;
 #pragma unroll
     for (int i = 0; i < 24; ++i) {  // channels 2i, 2i+1 against 2i+48, 2i+49
-      float first[2] = {bf16_lo(y[i]), bf16_hi(y[i])};
-      float second[2] = {bf16_lo(y[i + 24]), bf16_hi(y[i + 24])};
+      float f[2][4];  // [channel][f00, f01, f10, f11]
+      if (packed && rope_dtype == H3S_BF16) {
+        const uint4 w = __ldg(reinterpret_cast<const uint4 *>(rope_row) + i);
+        f[0][0] = bf16_lo(w.x); f[0][1] = bf16_hi(w.x); f[0][2] = bf16_lo(w.y); f[0][3] = bf16_hi(w.y);
+        f[1][0] = bf16_lo(w.z); f[1][1] = bf16_hi(w.z); f[1][2] = bf16_lo(w.w); f[1][3] = bf16_hi(w.w);
+      } else if (packed) {
+        const float4 a = __ldg(reinterpret_cast<const float4 *>(rope_row) + 2 * i);
+        const float4 b = __ldg(reinterpret_cast<const float4 *>(rope_row) + 2 * i + 1);
+        f[0][0] = a.x; f[0][1] = a.y; f[0][2] = a.z; f[0][3] = a.w;
+        f[1][0] = b.x; f[1][1] = b.y; f[1][2] = b.z; f[1][3] = b.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int64_t at = (2 * i + e) * stride_dim;
+          f[e][0] = rope_load(rope_row, at, rope_dtype);
+          f[e][1] = rope_load(rope_row, at + stride_pair, rope_dtype);
+          f[e][2] = rope_load(rope_row, at + stride_rot, rope_dtype);
+          f[e][3] = rope_load(rope_row, at + stride_rot + stride_pair, rope_dtype);
+        }
+      }
+      const float first[2] = {bf16_lo(y[i]), bf16_hi(y[i])};
+      const float second[2] = {bf16_lo(y[i + 24]), bf16_hi(y[i + 24])};
       float out_first[2], out_second[2];
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const int64_t at = (2 * i + e) * stride_dim;
-        const float f00 = rope_load(rope_row, at, rope_dtype);
-        const float f01 = rope_load(rope_row, at + stride_pair, rope_dtype);
-        const float f10 = rope_load(rope_row, at + stride_rot, rope_dtype);
-        const float f11 = rope_load(rope_row, at + stride_rot + stride_pair, rope_dtype);
-        out_first[e] = __fadd_rn(__fmul_rn(f00, first[e]), __fmul_rn(f01, second[e]));
-        out_second[e] = __fadd_rn(__fmul_rn(f10, first[e]), __fmul_rn(f11, second[e]));
+        out_first[e] = __fadd_rn(__fmul_rn(f[e][0], first[e]), __fmul_rn(f[e][1], second[e]));
+        out_second[e] = __fadd_rn(__fmul_rn(f[e][2], first[e]), __fmul_rn(f[e][3], second[e]));
       }
       y[i] = pack_bf16x2(out_first[0], out_first[1]);
       y[i + 24] = pack_bf16x2(out_second[0], out_second[1]);

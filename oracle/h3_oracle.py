@@ -47,9 +47,9 @@ KV_TILE = 64
 HEAD_DIM = 128
 LOG2E = 1.4426950408889634
 FP8_E4M3_MAX = 448.0
-# FP8 probabilities are taken relative to 2^(ceil(rowmax) - 5): the largest is
-# in (16, 32], which leaves E4M3 (max 448, min normal 2^-6) eleven octaves below.
-P_EXPONENT_OFFSET = 5.0
+# FP8 probabilities are taken relative to 2^(ceil(rowmax) - 7): the largest is
+# in (64, 128], which leaves E4M3 (max 448, min normal 2^-6) thirteen octaves below.
+P_EXPONENT_OFFSET = 7.0
 
 
 # --------------------------------------------------------------------------
@@ -359,7 +359,7 @@ def sparse_attention_int8_fp8(
     de-quantised from the FP8 carrier, ``out = acc / l``.
 
     ``p_format='fp32'`` keeps P in FP32 (the gate the tolerance is stated for).
-    ``p_format='e4m3'`` rounds ``exp2(logit2 - ceil(rowmax) + 5)`` to FP8-E4M3
+    ``p_format='e4m3'`` rounds ``exp2(logit2 - ceil(rowmax) + 7)`` to FP8-E4M3
     before the product while the row sum stays FP32 - the arithmetic of the
     CUDA kernel's single-term mode.  ``p_format='e4m3x2'`` carries P as two
     E4M3 terms, ``hi`` = P truncated to 4 significant bits and ``lo`` =
