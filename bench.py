@@ -92,75 +92,71 @@ def attention_ops(spec, route, geo, heads):
 
 
 class ClockSampler:
+    """SM clock, power and throttle reasons of one GPU during the timed region.
+
+    The sampling runs in a child process (NVML handle opened once, three
+    read-only queries every 5 ms, each a few microseconds): a thread inside this
+    process competes with the launching thread for the interpreter lock and
+    stretched a 2.2 ms multi-GPU step to 4 ms, and `nvidia-smi -lms` re-reads
+    its whole field list every period.  `nvidia-smi -lms 100` remains the
+    fallback when the NVML bindings are missing."""
+
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    CHILD = r"""
+import sys, time
+import pynvml as nv
+nv.nvmlInit()
+h = nv.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+print("max", nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM), flush=True)
+while True:
+    print("%.6f %d %.1f %d" % (time.time(), nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM),
+                               nv.nvmlDeviceGetPowerUsage(h) / 1000.0, reasons(h)), flush=True)
+    time.sleep(0.005)
+"""
+    REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index):
         self.index = index
         self.proc = None
         self.file = None
-        self.thread = None
-        self.samples = []
-        self.stop_flag = False
-
-    # NVML (read-only queries) from a thread every ~2 ms when the bindings are
-    # there - a timed region of a few tens of milliseconds still gets samples -
-    # else nvidia-smi every 100 ms.
-    def _nvml_loop(self, nvml, handle):
-        reasons_fn = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
-            getattr(nvml, "nvmlDeviceGetCurrentClocksThrottleReasons")
-        bits = {
-            "hw_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
-            "hw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
-            "sw_thermal_slowdown": getattr(nvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
-            "sw_power_cap": getattr(nvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
-        }
-        while not self.stop_flag:
-            try:
-                sm = nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)
-                power = nvml.nvmlDeviceGetPowerUsage(handle) / 1000.0
-                mask = reasons_fn(handle)
-                self.samples.append((float(sm), power, [n for n, bit in bits.items() if mask & bit]))
-            except Exception:
-                break
-            time.sleep(0.002)
+        self.mode = None
+        self.t_begin = None
 
     def start(self):
+        """Spawn the sampler (call before the warm-up: the child needs a moment to import)."""
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".log", delete=False)
         try:
-            import pynvml as nvml
+            import pynvml  # noqa: F401  (only to know whether the child can use it)
 
-            nvml.nvmlInit()
-            handle = nvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.sm_max = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
-            import threading
-
-            self.thread = threading.Thread(target=self._nvml_loop, args=(nvml, handle), daemon=True)
-            self.thread.start()
+            self.proc = subprocess.Popen([sys.executable, "-c", self.CHILD, str(self.index)], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+            self.mode = "nvml"
+            deadline = time.time() + 10.0  # the child is sampling once its first lines are in the file
+            while time.time() < deadline and self.proc.poll() is None and os.path.getsize(self.file.name) < 64:
+                time.sleep(0.02)
             return
         except Exception:
-            self.thread = None
+            pass
         try:
-            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS, "--format=csv,noheader,nounits",
                  "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+            self.mode = "smi"
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        self.t_begin = time.time()
+
     def stop(self):
-        if self.thread is not None:
-            self.stop_flag = True
-            self.thread.join(timeout=2)
-            if not self.samples:
-                return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no NVML samples"}
-            reasons = sorted({r for _, _, rs in self.samples for r in rs})
-            return {"sm_mhz": statistics.median(s for s, _, _ in self.samples), "sm_max_mhz": self.sm_max,
-                    "power_w_max": max(p for _, p, _ in self.samples), "samples": len(self.samples),
-                    "reasons": reasons, "source": "NVML queries every 2 ms during the timed region"}
+        t_end = time.time()
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "nvidia-smi unavailable"}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no sampler available"}
+        if self.mode == "smi":
+            time.sleep(0.15)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -168,25 +164,43 @@ class ClockSampler:
             self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        sm, sm_max, power, reasons = [], [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.file.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0])); sm_max.append(float(parts[1])); power.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, value in zip(names, parts[3:7]):
-                if value.lower() == "active":
-                    reasons.add(name)
+        lines = self.file.read().splitlines()
         self.file.close()
         os.unlink(self.file.name)
+        sm, power, reasons, sm_max = [], [], set(), None
+        if self.mode == "nvml":
+            for line in lines:
+                parts = line.split()
+                if len(parts) == 2 and parts[0] == "max":
+                    sm_max = float(parts[1])
+                    continue
+                if len(parts) != 4:
+                    continue
+                stamp = float(parts[0])
+                if self.t_begin is not None and not (self.t_begin <= stamp <= t_end):
+                    continue
+                sm.append(float(parts[1])); power.append(float(parts[2]))
+                mask = int(parts[3])
+                reasons.update(name for name, bit in self.REASON_BITS.items() if mask & bit)
+            source = "NVML queries every 5 ms from a child process, samples inside the timed region"
+        else:
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            maxima = []
+            for line in lines:
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 7:
+                    continue
+                try:
+                    sm.append(float(parts[0])); maxima.append(float(parts[1])); power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                reasons.update(name for name, value in zip(names, parts[3:7]) if value.lower() == "active")
+            sm_max = max(maxima) if maxima else None
+            source = "nvidia-smi -lms 100"
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "no samples"}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(sm_max), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons), "source": "nvidia-smi -lms 100"}
+            return {"sm_mhz": None, "sm_max_mhz": sm_max, "reasons": [], "note": "no samples inside the timed region"}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": sm_max, "power_w_max": max(power),
+                "samples": len(sm), "reasons": sorted(reasons), "source": source}
 
 
 def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4):
@@ -278,10 +292,11 @@ def run_config2(args, spec):
             e[3].record(); marks.append(e)
         return out, prepared.sparse
 
+    sampler = ClockSampler(0); sampler.start()
     for _ in range(args.warmup):
         _, sparse = step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(0); sampler.start()
+    sampler.mark_begin()
     t0, t1 = events(); t0.record()
     for _ in range(args.steps):
         _, sparse = step(record=True)
@@ -466,12 +481,13 @@ def main():
 
     # ---- device-resident timing ----
     sparse = None
-    for _ in range(args.warmup):
-        _, sparse = step(q, k, v)
-    fence()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        _, sparse = step(q, k, v)
+    fence()
+    sampler.mark_begin()
     t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     t_begin.record()
     for _ in range(args.steps):
