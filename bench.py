@@ -512,7 +512,10 @@ def main():
     # ---- end to end with host buffers ----
     e2e = None
     if not args.skip_e2e:
-        out_host = torch.empty((1, spec.heads if world > 1 else h1 - h0, spec.sequence, HEAD_DIM),
+        # N > 1: the gathered layer output reaches the host once, from rank 0; the other ranks
+        # read back the heads they computed
+        full_back = world > 1 and rank == 0
+        out_host = torch.empty((1, spec.heads if full_back else h1 - h0, spec.sequence, HEAD_DIM),
                                dtype=torch.bfloat16).pin_memory()
         def e2e_step():
             if world == 1:
@@ -522,7 +525,7 @@ def main():
                 return
             qd, kd, vd = (t.to(device, non_blocking=True) for t in (q_host, k_host, v_host))
             out, _ = step(qd, kd, vd)
-            out_host.copy_(out, non_blocking=True)
+            out_host.copy_(out if full_back else out[:, h0:h1], non_blocking=True)
         for _ in range(max(1, min(args.warmup, 2))):
             e2e_step()
         fence()
@@ -535,11 +538,14 @@ def main():
         e2e_ms = torch.tensor([b0.elapsed_time(b1) / args.steps], dtype=torch.float64, device=device)
         if world > 1:
             dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+        moved = torch.tensor([3.0 * q_host.numel() * q_host.element_size(),
+                              float(out_host.numel() * out_host.element_size())], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(moved, op=dist.ReduceOp.SUM)
         e2e = {"value": total_ops / (float(e2e_ms[0]) * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": float(e2e_ms[0]),
                "api": "B200SparseBackend.forward_host (pinned host Q/K/V in, host output back, head chunks pipelined)"
-                      if world == 1 else "pinned host Q/K/V -> prepare + attention + exchange -> host output",
-               "h2d_bytes_per_step": 3 * q_host.numel() * q_host.element_size(),
-               "d2h_bytes_per_step": out_host.numel() * out_host.element_size()}
+                      if world == 1 else "pinned host Q/K/V of the local heads -> prepare + attention + exchange -> host (rank 0: whole output, others: their heads)",
+               "h2d_bytes_per_step": int(moved[0]), "d2h_bytes_per_step": int(moved[1])}
 
     if rank == 0:
         peaks, peak_source = measured_peaks()
