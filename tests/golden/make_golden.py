@@ -85,7 +85,7 @@ def router_case(ref, name, q, k, sequence, video_start, budget, out):
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference", default="/root/reference")
+    parser.add_argument("--reference", required=True, help="checkout of the reference pack (the directory holding h3_optimizations/)")
     parser.add_argument("--skip-config1", action="store_true")
     args = parser.parse_args()
     sys.path.insert(0, args.reference)
