@@ -91,7 +91,11 @@ convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride,
 
 constexpr int kGemmM = 128, kGemmN = 256, kGemmK = 128;  // K in bytes == int8 elements
 constexpr int kGemmStages = 4;
-constexpr int kGemmThreads = 192;
+// warps 0-3: epilogue of the tile's first 128 columns, 4: TMA, 5: MMA, 6-7: idle,
+// 8-11: epilogue of the second 128 columns (a warp may only touch the TMEM lanes
+// 32*(warp%4)..: two warps per lane quarter halve the epilogue's time, which
+// exceeds the MMA time of a tile once the norm and the rotation run in it)
+constexpr int kGemmThreads = 384;
 constexpr uint32_t kGemmABytes = kGemmM * kGemmK;  // 16384
 constexpr uint32_t kGemmBBytes = kGemmN * kGemmK;  // 32768
 constexpr uint32_t kGemmOffB = kGemmStages * kGemmABytes;
@@ -227,7 +231,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&sh.acc_full[i], 1);
-      ptx::mbar_init(&sh.acc_empty[i], 4);
+      ptx::mbar_init(&sh.acc_empty[i], 8);
     }
     sh.abort_word = 0;
     ptx::fence_mbar_init();
@@ -285,9 +289,11 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (ok) ptx::tc_commit(&sh.acc_full[a]);
       }
     }
-  } else {
-    // epilogue warps 0-3: thread <-> accumulator row
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+  } else if (warp < 4 || warp >= 8) {
+    // epilogue: thread <-> accumulator row, warp group <-> 128-column half of the tile
+    const int quarter = warp & 3;
+    const int gi = warp >= 8 ? 1 : 0;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t local = 0;
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
@@ -299,11 +305,10 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       }
       ptx::tc_fence_after();
-      const int row = tm * kGemmM + warp * 32 + lane;
+      const int row = tm * kGemmM + quarter * 32 + lane;
       const bool row_ok = row < prm.rows;
       const float xs = row_ok ? __ldg(prm.x_scale + row) : 0.f;
-#pragma unroll 1
-      for (int gi = 0; gi < kGemmN / H3S_HEAD_DIM; ++gi) {
+      {
         const int group_col0 = tn * kGemmN + gi * H3S_HEAD_DIM;
         const int group = group_col0 >> 7;  // 128-column group == (kind, head)
         const bool group_ok = group_col0 < prm.n_out;
