@@ -203,47 +203,73 @@ while True:
                 "samples": len(sm), "reasons": sorted(reasons), "source": source}
 
 
-def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4):
-    """The reference's torch path restated on the CPU (oracle port), on a bounded
-    sample: the first `heads` heads of the workload, router + float sparse
-    attention over every query tile.  Returns (TOPS, seconds per step,
-    description, threads)."""
-    from oracle import h3_oracle as oracle
+def host_threads():
+    """Every core this process may run on.  torch.distributed.run exports
+    OMP_NUM_THREADS=1, so the count is set explicitly rather than inherited."""
+    try:
+        count = len(os.sched_getaffinity(0))
+    except AttributeError:
+        count = os.cpu_count() or 1
+    torch.set_num_threads(max(1, count))
+    return torch.get_num_threads()
 
+
+def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4):
+    """The reference's own torch path on the host cores, on a bounded sample:
+    the first `heads` heads of the workload, `SparseTileRouter.build_lut`
+    (attention/sparse/router.py:248) + `sparse_float_reference`
+    (benchmarks/bench_sparse_backends.py:302-326) over every query tile, FP32,
+    run from the unmodified sources staged under oracle/_ref.  Without the
+    staged copy the CPU restatement of the same two functions runs instead
+    (kind "port").  Returns (TOPS, seconds per step, description, threads, kind)."""
+    from oracle import h3_oracle as oracle
+    from oracle import ref_bridge
+
+    threads = host_threads()
     q, k, v = workloads.structured_qkv(spec, seed=0, heads=range(heads))
     q, k, v = q.float(), k.float(), v.float()
     start, stop = spec.video_range
     geo = oracle.geometry(spec.sequence, start, stop)
+    use_ref = ref_bridge.available() and stop == spec.sequence
+    ref_layout = ref_bridge.layout(spec.sequence, spec.segments, spec.video_range, spec.video_shape, spec.audio_t)
+    router = ref_bridge.router_module().SparseTileRouter(q_tile=128, kv_tile=64) if use_ref else None
     subset = list(range(geo.q_tiles))
     times = []
     ops = 0
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        _, retained, selected, route = oracle.build_route(q, k, spec.sequence, start, budget, stop)
-        oracle.sparse_float_reference(q, k, v, geo, route, q_tile_subset=subset)
+        if use_ref:
+            lut, valid, _ = router.build_lut(q, k, ref_layout, budget)
+            ref_bridge.sparse_float_reference(q, k, v, lut, valid)
+        else:
+            _, _, _, route = oracle.build_route(q, k, spec.sequence, start, budget, stop)
+            oracle.sparse_float_reference(q, k, v, geo, route, q_tile_subset=subset)
         dt = time.perf_counter() - t0
         if it >= warmup:
             times.append(dt)
         if it == 0:
+            _, _, _, route = oracle.build_route(q, k, spec.sequence, start, budget, stop)
             ops = attention_ops(spec, route, geo, heads)
     sec = statistics.mean(times)
-    desc = ("heads 0-%d of %s (%d of %d heads): router + FP32 sparse attention over all %d query tiles"
-            % (heads - 1, spec.name, heads, spec.heads, geo.q_tiles))
-    return ops / sec / 1e12, sec, desc, torch.get_num_threads()
+    desc = ("heads 0-%d of %s (%d of %d heads): %s router + FP32 sparse attention over all %d query tiles, "
+            "throughput = the sample's algorithmic ops / its time"
+            % (heads - 1, spec.name, heads, spec.heads,
+               "the reference's own (oracle/_ref)" if use_ref else "restated (oracle port)", geo.q_tiles))
+    return ops / sec / 1e12, sec, desc, threads, "reference" if use_ref else "port"
 
 
 def run_reference(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    tops, sec, desc, threads = cpu_reference_sample(spec, args.budget, steps=max(1, args.steps),
-                                                    warmup=args.warmup, heads=1)
+    tops, sec, desc, threads, kind = cpu_reference_sample(spec, args.budget, steps=max(1, args.steps),
+                                                          warmup=args.warmup, heads=2)
     line = {
         "impl": "reference", "metric": METRIC, "value": tops, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_name(spec, args.budget), "sample": desc},
-        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": tops, "unit": UNIT, "cores": threads, "kind": kind, "sample": desc},
         "e2e": {"value": tops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -581,8 +607,8 @@ def main():
         if e2e is not None:
             line["e2e"] = e2e
         if world == 1 and not args.skip_cpu_baseline:
-            tops, sec, desc, threads = cpu_reference_sample(spec, args.budget, heads=8)
-            line["cpu_baseline"] = {"value": tops, "unit": UNIT, "cores": threads, "kind": "port",
+            tops, sec, desc, threads, kind = cpu_reference_sample(spec, args.budget, heads=8)
+            line["cpu_baseline"] = {"value": tops, "unit": UNIT, "cores": threads, "kind": kind,
                                     "sample": desc, "seconds": sec}
         print(json.dumps(line))
     if world > 1:

@@ -100,12 +100,6 @@ __device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volati
   return __all_sync(0xffffffffu, ok);
 }
 
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float r;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
-  return r;
-}
-
 // packed fp32x2 arithmetic (one instruction for two lanes of a 64-bit register pair)
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -137,6 +131,51 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(b), "f"(a));
   asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(d), "f"(c));
   return static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+}
+
+// Constants of one tile's exponentials: x = c*f + bias (f carries the 1.5*2^23 offset).
+struct ExpArgs {
+  float2 c2, bias2;
+};
+
+// The int32 scores become fp32 without a conversion instruction: for |s| < 2^22,
+// bits(12582912.0f) + s are the bits of the float 12582912 + s exactly, and the
+// offset is folded into the constants of the FMA that follows.
+// kRagged (last KV tile of a sequence that is not a multiple of 64): keys from
+// n_valid on are masked, P = 0.
+template <bool kTwoTerm, bool kRagged>
+__device__ __forceinline__ float exp_and_pack(const uint32_t (&s)[64], const ExpArgs &a, int n_valid,
+                                              uint32_t (&packed)[16], uint32_t (&packed_lo)[16]) {
+  const float2 minus1 = make_float2(-1.f, -1.f);
+  float2 sum2 = make_float2(0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < 64; i += 4) {
+    float f[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      f[k] = __uint_as_float(s[i + k] + 0x4b400000u);
+      if (kRagged && i + k >= n_valid) f[k] = -INFINITY;
+    }
+    const float2 x01 = fma2(a.c2, make_float2(f[0], f[1]), a.bias2);
+    const float2 x23 = fma2(a.c2, make_float2(f[2], f[3]), a.bias2);
+    const float2 p01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
+    const float2 p23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
+    sum2 = add2(sum2, p01);
+    sum2 = add2(sum2, p23);
+    if (kTwoTerm) {
+      const float2 h01 = make_float2(__uint_as_float(__float_as_uint(p01.x) & 0xfff00000u),
+                                     __uint_as_float(__float_as_uint(p01.y) & 0xfff00000u));
+      const float2 h23 = make_float2(__uint_as_float(__float_as_uint(p23.x) & 0xfff00000u),
+                                     __uint_as_float(__float_as_uint(p23.y) & 0xfff00000u));
+      const float2 r01 = fma2(h01, minus1, p01);
+      const float2 r23 = fma2(h23, minus1, p23);
+      packed[i >> 2] = pack_e4m3x4(h01.x, h01.y, h23.x, h23.y);
+      packed_lo[i >> 2] = pack_e4m3x4(r01.x, r01.y, r23.x, r23.y);
+    } else {
+      packed[i >> 2] = pack_e4m3x4(p01.x, p01.y, p23.x, p23.y);
+    }
+  }
+  return sum2.x + sum2.y;
 }
 
 template <typename OutT> __device__ __forceinline__ void store_out8(OutT *dst, const float (&v)[8]);
@@ -310,11 +349,13 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (ptx::elect_one()) {
           const uint64_t v_desc = v_desc0 + static_cast<uint64_t>(s * (kVBytes >> 4));
 #pragma unroll
-          for (int term = 0; term < (kSplitP ? 2 : 1); ++term) {
+          for (int k = 0; k < H3S_KV_TILE / 32; ++k)
+            ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + k * 8, v_desc + 2 * k, idesc_pv,
+                            (i > 0 || k > 0) ? 1u : 0u);
+          if (kSplitP) {
 #pragma unroll
             for (int k = 0; k < H3S_KV_TILE / 32; ++k)
-              ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + term * 16 + k * 8, v_desc + 2 * k, idesc_pv,
-                              (i > 0 || k > 0 || term > 0) ? 1u : 0u);
+              ptx::umma_f8_ts(tmem_o, tmem_s + b * H3S_KV_TILE + 16 + k * 8, v_desc + 2 * k, idesc_pv, 1u);
           }
           ptx::tc_commit(&sh.kv_empty[s]);
           ptx::tc_commit(&sh.p_empty[b]);
@@ -351,33 +392,29 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       const float c = q_scale * sh.tile_scale[j % kStages];
       const int n_valid = min(H3S_KV_TILE, prm.sequence - t * H3S_KV_TILE);
 
-      // int32 scores -> fp32 without a conversion instruction: for |s| < 2^22,
-      // bits(12582912.0f) + s are the bits of the float 12582912 + s exactly, and
-      // the bias is folded into the FMA constant below.  Integer adds can issue
-      // on either the ALU or the FMA pipe.  Keys beyond the sequence (ragged
-      // last tile only) become -inf: out of the maximum, P = 0.
-      float f[64];
-#pragma unroll
-      for (int i = 0; i < 64; ++i) f[i] = __uint_as_float(s[i] + 0x4b400000u);
+      // Keys beyond the sequence (ragged last tile only) get the most negative
+      // score, which keeps them out of the maximum; the exponential loop sets
+      // their P to 0.
       if (n_valid < H3S_KV_TILE) {
 #pragma unroll
         for (int i = 0; i < 64; ++i)
-          if (i >= n_valid) f[i] = -INFINITY;
+          if (i >= n_valid) s[i] = 0x80000000u;
       }
-      // four independent chains of 3-input maxima (a single chain of 32 dependent
-      // instructions costs more than the arithmetic)
-      float fm0 = max3(f[0], f[1], f[2]), fm1 = max3(f[3], f[4], f[5]);
-      float fm2 = max3(f[6], f[7], f[8]), fm3 = max3(f[9], f[10], f[11]);
+      // row maximum on the raw integers (3-input integer max), four independent
+      // chains: a single chain of 32 dependent instructions costs more than the
+      // arithmetic
+      int im0 = __vimax3_s32(s[0], s[1], s[2]), im1 = __vimax3_s32(s[3], s[4], s[5]);
+      int im2 = __vimax3_s32(s[6], s[7], s[8]), im3 = __vimax3_s32(s[9], s[10], s[11]);
 #pragma unroll
       for (int i = 12; i + 7 < 64; i += 8) {
-        fm0 = max3(fm0, f[i], f[i + 1]);
-        fm1 = max3(fm1, f[i + 2], f[i + 3]);
-        fm2 = max3(fm2, f[i + 4], f[i + 5]);
-        fm3 = max3(fm3, f[i + 6], f[i + 7]);
+        im0 = __vimax3_s32(im0, s[i], s[i + 1]);
+        im1 = __vimax3_s32(im1, s[i + 2], s[i + 3]);
+        im2 = __vimax3_s32(im2, s[i + 4], s[i + 5]);
+        im3 = __vimax3_s32(im3, s[i + 6], s[i + 7]);
       }
-      fm0 = max3(fm0, f[60], f[61]);
-      fm1 = max3(fm1, f[62], f[63]);
-      const float fm = max3(fm0, fm1, fmaxf(fm2, fm3)) - kIntBias;
+      im0 = __vimax3_s32(im0, s[60], s[61]);
+      im1 = __vimax3_s32(im1, s[62], s[63]);
+      const float fm = static_cast<float>(__vimax3_s32(im0, im1, max(im2, im3)));
       const float mx = c * fm;  // c > 0
       const bool need = mx > m_used + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
@@ -404,39 +441,22 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         m_used = m_new;
       }
 
-      // P = exp2(c*f - m) two elements per instruction (packed fp32x2 FMA/ADD),
-      // hi = P truncated to 4 significant bits (exact in E4M3), lo = P - hi
-      const float bias = -fmaf(c, kIntBias, m_used);  // x = c*(f - 12582912) - m
-      const float2 c2 = make_float2(c, c), negm2 = make_float2(bias, bias), minus1 = make_float2(-1.f, -1.f);
-      float2 sum2 = make_float2(0.f, 0.f);
+      // P = exp2(c*f - m), two elements per instruction (packed fp32x2 FMA/ADD);
+      // x = c*(f - 12582912) - m
+      const float bias = -fmaf(c, kIntBias, m_used);
+      ExpArgs args;
+      args.c2 = make_float2(c, c);
+      args.bias2 = make_float2(bias, bias);
       uint32_t packed[16];
-      uint32_t packed_lo[kSplitP ? 16 : 1];
-#pragma unroll
-      for (int i = 0; i < 64; i += 4) {
-        float2 x01 = fma2(c2, make_float2(f[i], f[i + 1]), negm2);
-        float2 x23 = fma2(c2, make_float2(f[i + 2], f[i + 3]), negm2);
-        float2 p01 = make_float2(fast_exp2(x01.x), fast_exp2(x01.y));
-        float2 p23 = make_float2(fast_exp2(x23.x), fast_exp2(x23.y));
-        sum2 = add2(sum2, p01);
-        sum2 = add2(sum2, p23);
-        if (kSplitP) {
-          const float2 h01 = make_float2(__uint_as_float(__float_as_uint(p01.x) & 0xfff00000u),
-                                         __uint_as_float(__float_as_uint(p01.y) & 0xfff00000u));
-          const float2 h23 = make_float2(__uint_as_float(__float_as_uint(p23.x) & 0xfff00000u),
-                                         __uint_as_float(__float_as_uint(p23.y) & 0xfff00000u));
-          const float2 r01 = fma2(h01, minus1, p01);
-          const float2 r23 = fma2(h23, minus1, p23);
-          packed[i >> 2] = pack_e4m3x4(h01.x, h01.y, h23.x, h23.y);
-          packed_lo[i >> 2] = pack_e4m3x4(r01.x, r01.y, r23.x, r23.y);
-        } else {
-          packed[i >> 2] = pack_e4m3x4(p01.x, p01.y, p23.x, p23.y);
-        }
-      }
-      l += sum2.x + sum2.y;
-
+      uint32_t packed_lo[16];
       // P(j) overwrites this thread's own lane of S buffer b (already in
       // registers).  The MMA that produced S(j) was issued after P.V(j-2), so
       // nothing still reads these columns.
+      if (n_valid < H3S_KV_TILE) {
+        l += exp_and_pack<kSplitP, true>(s, args, n_valid, packed, packed_lo);
+      } else {
+        l += exp_and_pack<kSplitP, false>(s, args, n_valid, packed, packed_lo);
+      }
       H3S_TMEM_ST16(tmem_s + lane_addr + b * H3S_KV_TILE, packed);
       if (kSplitP) H3S_TMEM_ST16(tmem_s + lane_addr + b * H3S_KV_TILE + 16, packed_lo);
       ptx::tmem_wait_st();
