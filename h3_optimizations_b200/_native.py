@@ -38,6 +38,8 @@ PROTOTYPES = {
     "h3s_abi_version": (c_int, []),
     "h3s_last_error": (c_char_p, []),
     "h3s_device_capability": (c_int, []),
+    "h3s_set_wait_budget_ns": (c_int, [ctypes.c_ulonglong]),
+    "h3s_get_wait_budget_ns": (ctypes.c_ulonglong, []),
     "h3s_column_stats_scratch_bytes": (c_size_t, [c_int]),
     "h3s_column_stats": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_int, c_int,
                                  c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -12,6 +12,15 @@ column statistics (K mean, V amax) -> INT8 Q/K blocks with FP64 tile means ->
 FP8 V carrier -> router.  ``execute`` launches the tcgen05 attention kernel.
 There is no fallback of any kind: a device that is not sm_100, a missing
 native library or a failed launch raises ``SparseSageError``.
+
+Every wait inside the attention kernel is bounded; a wait that runs out makes
+the kernel return early and leave a code in a per-device status word that the
+backend hands to every launch.  Reading that word needs the stream to have
+drained, so it is not done on the hot path: ``check_status()`` reads it (and
+raises) whenever the caller synchronises anyway, ``forward_host`` calls it
+before it returns, and the next ``prepare`` on the device looks at the word
+through a pinned mirror filled by an asynchronous copy queued after the
+previous launch, without blocking.
 """
 
 from __future__ import annotations
@@ -66,7 +75,7 @@ class B200SparseBackend:
 
             self.projector = ChunkedSparseQKVProjector()
         self.smooth_k = bool(smooth_k)
-        self._status = None
+        self._status = {}  # device index -> (device int32[4], pinned mirror, event of the last mirror copy)
 
     # -- identity ---------------------------------------------------------
 
@@ -183,10 +192,55 @@ class B200SparseBackend:
             streams[key] = torch.cuda.Stream(device)
         return streams[key]
 
+    # -- device status word -------------------------------------------------
+
+    ABORT_NAMES = {1: "Q tile load", 2: "K/V tile load", 3: "free K/V stage", 4: "QK^T result", 5: "P from the softmax warps",
+                   6: "free P buffer", 7: "P.V before a rescale", 8: "last P.V"}
+
+    def _status_slot(self, device):
+        key = device.index if device.index is not None else torch.cuda.current_device()
+        slot = self._status.get(key)
+        if slot is None:
+            word = torch.zeros(4, dtype=torch.int32, device=device)
+            mirror = torch.zeros(4, dtype=torch.int32).pin_memory()
+            slot = self._status[key] = (word, mirror, torch.cuda.Event())
+        return slot
+
+    @classmethod
+    def _raise_for(cls, words, where):
+        code, cta, head, tile = (int(x) for x in words)
+        if code != 0:
+            raise SparseSageError(
+                "Sparse attention kernel gave up waiting for %s (code %d) in CTA %d, head %d, query tile %d (%s); "
+                "the output of that launch is invalid"
+                % (cls.ABORT_NAMES.get(code, "an unknown event"), code, cta, head, tile, where))
+
+    def _poll_status(self, device):
+        """Non-blocking look at the mirror of the previous launch's status."""
+        slot = self._status.get(device.index if device.index is not None else torch.cuda.current_device())
+        if slot is not None and slot[2].query():
+            self._raise_for(slot[1].tolist(), "reported by an earlier launch")
+
+    def check_status(self, device=None):
+        """Synchronise with the device and raise ``SparseSageError`` if a
+        bounded device wait ran out in any attention launch since the last
+        check.  Clears the word."""
+        devices = list(self._status) if device is None else [torch.device(device).index]
+        for key in devices:
+            slot = self._status.get(key)
+            if slot is None:
+                continue
+            words = slot[0].cpu().tolist()
+            if words[0] != 0:
+                slot[0].zero_()
+                slot[1].zero_()
+            self._raise_for(words, "found by check_status")
+
     # -- protocol -------------------------------------------------------------
 
     def prepare(self, q, k, v, *, layer_index, transformer_options):
         heads, sequence = self._validate_qkv(q, k, v)
+        self._poll_status(q.device)
         snapshot = self._snapshot(transformer_options, sequence)
         video_budget = resolve_video_budget(
             self.config, snapshot.step_index, snapshot.total_steps, layer_index
@@ -205,20 +259,24 @@ class B200SparseBackend:
             side = self._side_stream(q.device)
             v_carrier = ops.allocate_v_carrier(sequence, heads, v.device)
             side.wait_stream(main)
-            with torch.cuda.stream(side):
-                ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
-            q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
-            k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
-            if need_route:
-                route = self.router.build_route_from_summaries(
-                    q_summary, k_summary, snapshot.layout, video_budget,
-                    **self._sink(transformer_options, layer_index),
-                )
-            else:
-                route = self.router.build_route(
-                    q, k, snapshot.layout, video_budget, **self._sink(transformer_options, layer_index)
-                )
-            main.wait_stream(side)
+            try:
+                with torch.cuda.stream(side):
+                    ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
+                q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
+                k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
+                if need_route:
+                    route = self.router.build_route_from_summaries(
+                        q_summary, k_summary, snapshot.layout, video_budget,
+                        **self._sink(transformer_options, layer_index),
+                    )
+                else:
+                    route = self.router.build_route(
+                        q, k, snapshot.layout, video_budget, **self._sink(transformer_options, layer_index)
+                    )
+            finally:
+                # on every exit path the main stream is ordered after the V quantiser, so the
+                # allocator cannot hand v / v_scale / v_carrier to someone else while it still runs
+                main.wait_stream(side)
         except SparseRouterError as exc:
             raise SparseSageError("sparse routing failed: %s" % exc) from exc
         except _native.NativeError as exc:
@@ -279,14 +337,19 @@ class B200SparseBackend:
         sparse = prepared.sparse
         route = sparse.route
         geometry = route.geometry
+        device = sparse.q_int8.device
+        word, mirror, copied = self._status_slot(device)
         try:
             out_dtype = sparse.output_dtype
-            return ops.sparse_attention(
+            result = ops.sparse_attention(
                 sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale,
                 sparse.v_scale, route.indices,
                 q_start=geometry.pure_video_q_start, q_stop=geometry.pure_video_q_stop,
-                out=out, out_dtype=out_dtype,
+                out=out, out_dtype=out_dtype, status=word,
             )
+            mirror.copy_(word, non_blocking=True)  # 16 bytes, stream ordered behind the kernel
+            copied.record(torch.cuda.current_stream(device))
+            return result
         except _native.NativeError as exc:
             raise SparseSageError(
                 "Sparse attention kernel failed: layer=%d sequence=%d heads=%d dtype=%s: %s"
@@ -304,9 +367,10 @@ class B200SparseBackend:
         the device-to-host copy of the output of chunk c-1.  The PCIe input copy
         is the longest of the three, so the call takes about as long as that
         copy alone.  Returns ``out`` (host, HND ``(1, H, S, 128)``; allocated
-        pinned when not given); it is complete once the current stream is
-        synchronised.  With a route sink installed the heads are not split (the
-        sink expects one call per layer)."""
+        pinned when not given).  With a route sink installed the heads are not
+        split (the sink expects one call per layer).  The call returns once the
+        output is in host memory and raises if a launch reported an expired
+        device wait."""
         if q.is_cuda or k.is_cuda or v.is_cuda:
             raise SparseSageError("forward_host expects host tensors; use prepare/execute for device tensors")
         if q.shape != k.shape or q.shape != v.shape or q.ndim != 4 or q.shape[0] != 1 or q.shape[3] != 128:
@@ -351,6 +415,8 @@ class B200SparseBackend:
                 slot["stored"].record(d2h)
         main.wait_stream(d2h)
         main.wait_stream(h2d)
+        main.synchronize()  # the result lives in host memory: it is complete when the call returns
+        self.check_status(device)
         return out
 
     def _host_pipeline(self, device, chunk, sequence, dtype, n_slots):

@@ -69,6 +69,14 @@ struct AttnParams {
   // plain stores), so no separate gather pass is needed
   void *peer_out[H3S_MAX_PEER_OUTPUTS];
   int n_peer_out;
+  // Bound of the waits for TMA loads; a wait further down the pipeline (QK^T
+  // result 2x, P 3x, P.V and free stages 4x) gets a multiple, so that when a
+  // stage stalls the wait closest to the cause is the one that runs out first
+  // and names it in the status words.
+  unsigned long long wait_budget_ns;
+  // self-test of the bounded waits (H3S_ATTN_TEST_DROP_KV_LOAD): the producer
+  // never issues the K/V load of this iteration, so the wait for it runs out
+  int drop_kv_load;                   // iteration index, -1 = none
 };
 
 struct AttnShared {
@@ -95,8 +103,9 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Every lane polls the barrier; the warp then agrees on the outcome so that
 // the .sync.aligned tcgen05 instructions that follow stay convergent even if
 // the abort word was raised between two lanes' polls.
-__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word, int code) {
-  const bool ok = ptx::mbar_wait(bar, parity, abort_word, code);
+__device__ __forceinline__ bool warp_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word, int code,
+                                          unsigned long long budget_ns) {
+  const bool ok = ptx::mbar_wait(bar, parity, abort_word, code, budget_ns);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -295,8 +304,8 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
           const int j = j0 + i;
           const int s = j % kStages;
           const uint32_t use = static_cast<uint32_t>(j / kStages);
-          ok = ptx::mbar_wait(&sh.kv_empty[s], (use & 1u) ^ 1u, abort_word, kAbortKvEmpty);
-          if (ok) {
+          ok = ptx::mbar_wait(&sh.kv_empty[s], (use & 1u) ^ 1u, abort_word, kAbortKvEmpty, 4 * prm.wait_budget_ns);
+          if (ok && j != prm.drop_kv_load) {
             sh.tile_index[s] = t;
             sh.tile_scale[s] = ks;
             ptx::mbar_arrive_expect_tx(&sh.kv_full[s], kKBytes + kVBytes);
@@ -328,9 +337,9 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       };
       auto wait_stage = [&](int j) {
         return warp_wait(&sh.kv_full[j % kStages], static_cast<uint32_t>(j / kStages) & 1u, abort_word,
-                         kAbortKvFull);
+                         kAbortKvFull, prm.wait_budget_ns);
       };
-      bool ok = warp_wait(&sh.q_full, 0, abort_word, kAbortQFull);
+      bool ok = warp_wait(&sh.q_full, 0, abort_word, kAbortQFull, prm.wait_budget_ns);
       for (int j = 0; ok && j < min(2, n_iter); ++j) {
         ok = wait_stage(j);
         if (ok) {
@@ -341,7 +350,7 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       for (int i = 0; ok && i < n_iter; ++i) {
         const int s = i % kStages, b = i & 1;
         if (i + 2 < n_iter && !wait_stage(i + 2)) { ok = false; break; }
-        if (!warp_wait(&sh.p_full[b], static_cast<uint32_t>(i >> 1) & 1u, abort_word, kAbortPFull)) {
+        if (!warp_wait(&sh.p_full[b], static_cast<uint32_t>(i >> 1) & 1u, abort_word, kAbortPFull, 3 * prm.wait_budget_ns)) {
           ok = false;
           break;
         }
@@ -376,7 +385,7 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     for (int j = 0; j < n_iter; ++j) {
       const int b = j & 1;
       const uint32_t use = static_cast<uint32_t>(j >> 1);
-      if (!warp_wait(&sh.s_full[b], use & 1u, abort_word, kAbortSFull)) { ok = false; break; }
+      if (!warp_wait(&sh.s_full[b], use & 1u, abort_word, kAbortSFull, 2 * prm.wait_budget_ns)) { ok = false; break; }
       ptx::tc_fence_after();
       uint32_t s[64];
       H3S_TMEM_LD32(tmem_s + lane_addr + b * H3S_KV_TILE, s);
@@ -423,7 +432,7 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
         if (j > 0) {
           const int pb = (j - 1) & 1;
           const uint32_t pu = static_cast<uint32_t>((j - 1) >> 1);
-          if (!warp_wait(&sh.p_empty[pb], pu & 1u, abort_word, kAbortPvDone)) { ok = false; break; }
+          if (!warp_wait(&sh.p_empty[pb], pu & 1u, abort_word, kAbortPvDone, 4 * prm.wait_budget_ns)) { ok = false; break; }
           ptx::tc_fence_after();
 #pragma unroll 1
           for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
@@ -467,7 +476,7 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
 
     if (ok) {
       const int last = n_iter - 1;
-      ok = warp_wait(&sh.p_empty[last & 1], static_cast<uint32_t>(last >> 1) & 1u, abort_word, kAbortFinal);
+      ok = warp_wait(&sh.p_empty[last & 1], static_cast<uint32_t>(last >> 1) & 1u, abort_word, kAbortFinal, 4 * prm.wait_budget_ns);
     }
     if (ok) {
       // Epilogue: O * v_scale / l -> OutT, staged through shared memory (the K
@@ -631,6 +640,8 @@ static int sparse_attn_fwd_impl(const int8_t *q8, const int8_t *k8, const uint8_
   prm.q_tiles = ceil_div(sequence, H3S_Q_TILE); prm.kv_tiles = ceil_div(sequence, H3S_KV_TILE);
   prm.out_dtype = out_dtype;
   prm.n_peer_out = n_peer_out;
+  prm.wait_budget_ns = wait_budget_ns();
+  prm.drop_kv_load = (flags & H3S_ATTN_TEST_DROP_KV_LOAD) ? 0 : -1;
   for (int i = 0; i < H3S_MAX_PEER_OUTPUTS; ++i) prm.peer_out[i] = i < n_peer_out ? peer_out[i] : nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool split_p = (flags & H3S_ATTN_P_SINGLE) == 0;

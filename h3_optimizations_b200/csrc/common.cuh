@@ -27,6 +27,10 @@ int fail(int code, const char *fmt, ...);
                          cudaGetErrorString(err__));                           \
   } while (0)
 
+// Upper bound of every device-side wait of the kernels launched from now on
+// (h3s_set_wait_budget_ns).
+unsigned long long wait_budget_ns();
+
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // ---- element loads: 8 consecutive channels of one row, widened to fp32 ----

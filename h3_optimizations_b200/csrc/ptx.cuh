@@ -1,10 +1,11 @@
 // Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor),
 // tcgen05 (TMEM allocation, MMA, commit, ld/st) and UMMA descriptors.
 //
-// Every wait is bounded: `mbar_wait` gives up after kWaitBudgetNs on the
-// global timer or as soon as another thread of the CTA has raised the abort
-// word, so a protocol error ends the kernel with a status code instead of
-// hanging the GPU.
+// Every wait is bounded: `mbar_wait` gives up after `budget_ns` on the global
+// timer (the launch passes h3s_set_wait_budget_ns's value, kWaitBudgetNs by
+// default) or as soon as another thread of the CTA has raised the abort word,
+// so a protocol error ends the kernel with a status code instead of hanging
+// the GPU.
 #pragma once
 
 #include <cuda.h>
@@ -14,7 +15,7 @@
 namespace h3s {
 namespace ptx {
 
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s
+constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s, the default budget
 // A failed try_wait parks the thread in hardware for up to this long (it wakes
 // as soon as the phase completes), so waiting warps do not burn issue slots.
 constexpr uint32_t kSuspendHintNs = 20000u;
@@ -97,7 +98,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
 // *abort_word with `code`) when the budget expires or another waiter already
 // gave up.  `abort_word` lives in shared memory.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_word,
-                                          int code) {
+                                          int code, unsigned long long budget_ns) {
   // a phase that is already complete costs one test_wait (a try_wait with a
   // suspend hint takes about twice as long even when it succeeds at once)
   if (mbar_test_wait(bar, parity)) return true;
@@ -107,7 +108,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 15u) == 0u) {
       if (*abort_word != 0) return false;
-      if (global_timer_ns() - start > kWaitBudgetNs) {
+      if (global_timer_ns() - start > budget_ns) {
         atomicCAS(const_cast<int *>(abort_word), 0, code);
         return false;
       }

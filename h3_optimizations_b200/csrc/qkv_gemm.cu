@@ -9,7 +9,7 @@
 //                        128x256 tiles, K step 128 bytes (SWIZZLE_128B), 4-stage
 //                        TMA ring, two TMEM accumulators so the epilogue of one
 //                        tile overlaps the MMAs of the next.  The epilogue
-//                        de-quantises (acc * x_scale[row] * w_scale[col]), rounds
+//                        de-quantises (acc * (x_scale[row] * w_scale[col])), rounds
 //                        to bf16 and scatters into head-major (3*H, rows, 128)
 //                        staging that the carrier kernels consume.
 #include "common.cuh"
@@ -130,6 +130,7 @@ struct GemmParams {
   int rope_dtype;         // H3S_F32 or H3S_BF16
   int heads;
   float epsilon;
+  unsigned long long wait_budget_ns;  // bound of every mbarrier wait
 };
 
 __device__ __forceinline__ float rope_load(const void *base, int64_t index, int dtype) {
@@ -256,7 +257,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kGemmStages;
           const uint32_t use = it / kGemmStages;
-          if (!ptx::mbar_wait(&sh.empty[s], (use & 1u) ^ 1u, abort_word, kGemmAbortEmpty)) { ok = false; break; }
+          if (!ptx::mbar_wait(&sh.empty[s], (use & 1u) ^ 1u, abort_word, kGemmAbortEmpty, prm.wait_budget_ns)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(&sh.full[s], kGemmABytes + kGemmBBytes);
           ptx::tma_load_2d(smem + s * kGemmABytes, &map_a, &sh.full[s], ks * kGemmK, tm * kGemmM);
           ptx::tma_load_2d(smem + kGemmOffB + s * kGemmBBytes, &map_b, &sh.full[s], ks * kGemmK, tn * kGemmN);
@@ -271,12 +272,12 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
         const int a = local & 1;
         const uint32_t acc_use = local >> 1;
-        if (!ptx::mbar_wait(&sh.acc_empty[a], (acc_use & 1u) ^ 1u, abort_word, kGemmAbortAccEmpty)) { ok = false; break; }
+        if (!ptx::mbar_wait(&sh.acc_empty[a], (acc_use & 1u) ^ 1u, abort_word, kGemmAbortAccEmpty, prm.wait_budget_ns)) { ok = false; break; }
         ptx::tc_fence_after();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
           const int s = it % kGemmStages;
           const uint32_t use = it / kGemmStages;
-          if (!ptx::mbar_wait(&sh.full[s], use & 1u, abort_word, kGemmAbortFull)) { ok = false; break; }
+          if (!ptx::mbar_wait(&sh.full[s], use & 1u, abort_word, kGemmAbortFull, prm.wait_budget_ns)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::umma_desc_kmajor(ptx::smem_u32(smem + s * kGemmABytes), 1024, ptx::kSwizzle128);
           const uint64_t b_desc =
@@ -301,7 +302,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int a = local & 1;
       const uint32_t acc_use = local >> 1;
       {
-        const bool got = ptx::mbar_wait(&sh.acc_full[a], acc_use & 1u, abort_word, kGemmAbortAccFull);
+        const bool got = ptx::mbar_wait(&sh.acc_full[a], acc_use & 1u, abort_word, kGemmAbortAccFull, prm.wait_budget_ns);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       }
       ptx::tc_fence_after();
@@ -328,8 +329,9 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 uint32_t *wp = reinterpret_cast<uint32_t *>(&w);
 #pragma unroll
                 for (int e = 0; e < 8; e += 2) {
-                  const float y0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e])), xs), __ldg(prm.w_scale + col0 + i + e));
-                  const float y1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + e + 1])), xs), __ldg(prm.w_scale + col0 + i + e + 1));
+                  // acc * (row_scale * column_scale), the product of the scales first (fused_qkv.py:222,424)
+                  const float y0 = __fmul_rn(static_cast<float>(static_cast<int>(acc[i + e])), __fmul_rn(xs, __ldg(prm.w_scale + col0 + i + e)));
+                  const float y1 = __fmul_rn(static_cast<float>(static_cast<int>(acc[i + e + 1])), __fmul_rn(xs, __ldg(prm.w_scale + col0 + i + e + 1)));
                   const __nv_bfloat162 t = __floats2bfloat162_rn(y0, y1);
                   wp[e >> 1] = *reinterpret_cast<const uint32_t *>(&t);
                 }
@@ -349,8 +351,8 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             for (int i = 0; i < 32; i += 2) {
               const float2 ws = __ldg(reinterpret_cast<const float2 *>(prm.w_scale + group_col0 + cc * 32 + i));
               y[cc * 16 + (i >> 1)] =
-                  pack_bf16x2(__fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i])), xs), ws.x),
-                              __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int>(acc[i + 1])), xs), ws.y));
+                  pack_bf16x2(__fmul_rn(static_cast<float>(static_cast<int>(acc[i])), __fmul_rn(xs, ws.x)),
+                              __fmul_rn(static_cast<float>(static_cast<int>(acc[i + 1])), __fmul_rn(xs, ws.y)));
             }
           }
           if (row_ok && group_ok) {
@@ -466,6 +468,7 @@ static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const i
   prm.rope_stride_seq = rope ? rope_strides[0] : 0; prm.rope_stride_dim = rope ? rope_strides[1] : 0;
   prm.rope_stride_rot = rope ? rope_strides[2] : 0; prm.rope_stride_pair = rope ? rope_strides[3] : 0;
   prm.heads = heads; prm.epsilon = epsilon;
+  prm.wait_budget_ns = wait_budget_ns();
   int device = 0, sms = 0;
   H3S_CHECK_CUDA(cudaGetDevice(&device));
   H3S_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));

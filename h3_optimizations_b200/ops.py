@@ -20,6 +20,7 @@ KV_TILE = 64
 HEAD_DIM = 128
 FP8_V_BOUND = 448.0
 ATTN_P_SINGLE = 1
+ATTN_TEST_DROP_KV_LOAD = 0x4000
 
 
 def _ceil_div(a, b):
@@ -39,6 +40,15 @@ def device_capability():
     if code < 0:
         check(code, "h3s_device_capability")
     return code
+
+
+def set_wait_budget_ns(nanoseconds):
+    """Bound of every device-side wait of the kernels launched from now on
+    (default 2 s).  Returns the previous value."""
+    lib = _native.load()
+    previous = int(lib.h3s_get_wait_budget_ns())
+    check(lib.h3s_set_wait_budget_ns(int(nanoseconds)), "h3s_set_wait_budget_ns")
+    return previous
 
 
 def column_stats(k=None, v=None, v_bound=FP8_V_BOUND):
@@ -330,7 +340,7 @@ def new_attention_output(heads, sequence, dtype, device):
 
 def sparse_attention(q8, k8, v_carrier, q_scale, k_scale, v_scale, route=None, *, q_start=0, q_stop=0,
                      out=None, out_dtype=torch.bfloat16, status=None, legacy_mma=False, single_term_p=False,
-                     peer_out_ptrs=None):
+                     peer_out_ptrs=None, extra_flags=0):
     """Launch the attention kernel.  Returns ``out`` (HND).  ``single_term_p``
     carries the probabilities as one E4M3 term instead of hi + lo.
     ``peer_out_ptrs``: device addresses (ints) of up to 7 further buffers,
@@ -344,7 +354,7 @@ def sparse_attention(q8, k8, v_carrier, q_scale, k_scale, v_scale, route=None, *
         ptr(q8), ptr(k8), ptr(v_carrier), ptr(q_scale), ptr(k_scale), ptr(v_scale), ptr(route), route_len,
         int(q_start), int(q_stop), ptr(out), dtype_code(out.dtype), out.stride(1), out.stride(2), heads, sequence,
     )
-    flags = ATTN_P_SINGLE if single_term_p else 0
+    flags = (ATTN_P_SINGLE if single_term_p else 0) | int(extra_flags)
     if peer_out_ptrs:
         if legacy_mma:
             raise _native.NativeError("sparse_attention: the cross-check kernel does not scatter to peers")

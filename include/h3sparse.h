@@ -158,7 +158,7 @@ int h3s_convrot_quant_rows(const void *x, int64_t x_stride_row, int rows,
 
 /*
  * INT8 GEMM + de-quantisation for one chunk (tcgen05 kind::i8, TMA fed):
- *   y[row, n] = bf16( float(sum_k x_i8[row,k] * w_i8[n,k]) * x_scale[row] * w_scale[n] )
+ *   y[row, n] = bf16( float(sum_k x_i8[row,k] * w_i8[n,k]) * (x_scale[row] * w_scale[n]) )
  * w_i8 int8 (n_out, hidden) contiguous, rows ordered [Q heads | K heads | V heads]
  * (row kind*H*128 + head*128 + d); n_out and hidden multiples of 128.
  * Output is head-major: 128-column group g (= kind*H + head) of row r lands at
@@ -180,7 +180,7 @@ int h3s_qkv_gemm_chunk(const int8_t *x_i8, const float *x_scale,
 /*
  * The same GEMM with the per-head RMS norm and the split-half rotary embedding
  * of the Q and K heads applied in its epilogue (V heads pass through):
- *   y    = bf16(acc * x_scale[row] * w_scale[col])
+ *   y    = bf16(acc * (x_scale[row] * w_scale[col]))
  *   y    = bf16(y * rsqrt(mean_d(y^2) + epsilon) * norm[d])       norm = q_norm | k_norm, fp32 (128)
  *   y[d], y[d+48] = bf16(f00*y[d] + f01*y[d+48]), bf16(f10*y[d] + f11*y[d+48])   for d < 48
  * with f(a,b) = rope[row*rope_strides[0] + d*rope_strides[1] + a*rope_strides[2]
@@ -231,9 +231,28 @@ int h3s_route_to_delta_lut(const int32_t *route, int heads, int q_tiles,
                            int route_len, int32_t *lut, int32_t *valid,
                            h3s_stream_t stream);
 
+/*
+ * Upper bound, in nanoseconds, of every wait inside the tcgen05 kernels
+ * (attention and QKV GEMM) launched after the call; default 2 s, accepted range
+ * 1 us .. 60 s.  A wait that runs out ends the kernel with a code in the
+ * launch's status words (attention: 1 Q tile load, 2 K/V tile load, 3 free
+ * K/V stage, 4 QK^T result, 5 P from the softmax warps, 6 free P buffer,
+ * 7 P.V before a rescale, 8 last P.V; GEMM: 21 operand stage, 22 free stage,
+ * 23 accumulator, 24 free accumulator), followed by the CTA index and, for
+ * attention, the head and the query tile.  Process-wide.  No counterpart in
+ * the reference (its Triton kernels have no device-side waits).
+ */
+int h3s_set_wait_budget_ns(unsigned long long nanoseconds);
+unsigned long long h3s_get_wait_budget_ns(void);
+
 /* Attention ------------------------------------------------------------- */
 
 #define H3S_ATTN_P_SINGLE 1
+/* Self-test of the bounded device waits: the K/V load of the first iteration is
+ * never issued, so the wait for it gives up after the wait budget, the kernel
+ * writes its status words, releases its tensor memory and returns.  The output
+ * of such a launch is meaningless.  Nothing faults and nothing hangs. */
+#define H3S_ATTN_TEST_DROP_KV_LOAD 0x4000
 #define H3S_MAX_PEER_OUTPUTS 7
 
 /*

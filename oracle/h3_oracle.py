@@ -484,11 +484,11 @@ def convrot_quantize_rows(x, group=256):
 
 
 def qkv_project_int8(x_i8, x_scale, w_i8, w_scale, out_dtype=torch.bfloat16):
-    """``y = bf16(float(int32 x.wT) * x_scale[row] * w_scale[col])``.
-    attention/sparse/fused_qkv.py:198-223.  Integer GEMM evaluated exactly in
-    FP64 (|acc| <= 127*127*3072 < 2^53)."""
+    """``y = bf16(float(int32 x.wT) * (x_scale[row] * w_scale[col]))``, the
+    product of the two scales taken first (attention/sparse/fused_qkv.py:198-223,
+    line 222).  Integer GEMM evaluated exactly in FP64 (|acc| <= 127*127*3072 < 2^53)."""
     acc = (x_i8.double() @ w_i8.double().T).to(torch.float32)
-    y = acc * x_scale[:, None] * w_scale[None, :]
+    y = acc * (x_scale[:, None] * w_scale[None, :])
     return y.to(out_dtype)
 
 
