@@ -25,6 +25,17 @@ DTYPE_CODES = {
 ABI_VERSION = 1
 
 
+class QKVCarriers(ctypes.Structure):
+    """``h3s_qkv_carriers`` of include/h3sparse.h."""
+
+    _fields_ = [
+        ("q8", c_void_p), ("q_scale", c_void_p), ("q_summary", c_void_p),
+        ("k8", c_void_p), ("k_scale", c_void_p), ("k_summary", c_void_p),
+        ("k_stage", c_void_p), ("v_stage", c_void_p), ("stats", c_void_p),
+        ("summary_dtype", c_int), ("sequence_total", c_int), ("row_start", c_int),
+    ]
+
+
 class NativeError(RuntimeError):
     """The native library is missing, mismatched, or a call failed."""
 
@@ -55,6 +66,10 @@ PROTOTYPES = {
     "h3s_qkv_gemm_chunk_norm_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                              c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p]),
+    "h3s_qkv_gemm_chunk_carriers": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                            ctypes.POINTER(QKVCarriers), c_void_p, c_void_p, c_float, c_void_p,
+                                            c_int, c_void_p, c_void_p, c_void_p]),
+    "h3s_column_stats_finalize": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "h3s_route_topk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_void_p]),
     "h3s_route_to_delta_lut": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,

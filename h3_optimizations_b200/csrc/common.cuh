@@ -116,8 +116,12 @@ __device__ __forceinline__ SharedDivisor make_divisor(float divisor) {
   return d;
 }
 
+// kExact is d.exact, tested ONCE by the caller around its whole element loop: with the
+// test inside `divide` the compiler keeps the IEEE division sequence in the loop body
+// next to the three-instruction path, which made the quantisers several times slower.
+template <bool kExact>
 __device__ __forceinline__ float divide(const SharedDivisor &d, float a) {
-  if (!d.exact) return __fdiv_rn(a, d.b);
+  if (!kExact) return __fdiv_rn(a, d.b);
   const float q0 = __fmul_rn(a, d.r);
   const float e = __fmaf_rn(-d.b, q0, a);
   return __fmaf_rn(e, d.r, q0);

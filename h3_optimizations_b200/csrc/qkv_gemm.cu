@@ -12,6 +12,13 @@
 //                        de-quantises (acc * (x_scale[row] * w_scale[col])), rounds
 //                        to bf16 and scatters into head-major (3*H, rows, 128)
 //                        staging that the carrier kernels consume.
+//   qkv_gemm_chunk_carriers : the same GEMM whose epilogue emits the carriers
+//                        themselves: INT8 Q blocks with scale and tile mean
+//                        (a 128-row Q block of one head is one accumulator
+//                        tile half), INT8 K half-blocks when K is not smoothed;
+//                        K (when smoothed) and V, which need whole-sequence
+//                        statistics, are staged as bf16 while their column sums
+//                        / maxima are accumulated for the short second phase.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tma.cuh"
@@ -73,11 +80,20 @@ convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride,
     const float scale = amax > 0.f ? __fdiv_rn(amax, 127.0f) : 1.0f;
     const SharedDivisor by_scale = make_divisor(scale);  // exact v/scale without a divide per element
     uint32_t packed[2] = {0u, 0u};
+    if (by_scale.exact) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      int code = __float2int_rn(divide(by_scale, v[i]));
-      code = max(-127, min(127, code));
-      packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+      for (int i = 0; i < 8; ++i) {
+        int code = __float2int_rn(divide<true>(by_scale, v[i]));
+        code = max(-127, min(127, code));
+        packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        int code = __float2int_rn(divide<false>(by_scale, v[i]));
+        code = max(-127, min(127, code));
+        packed[i >> 2] |= (static_cast<uint32_t>(code) & 0xffu) << ((i & 3) * 8);
+      }
     }
     *reinterpret_cast<uint2 *>(out + static_cast<int64_t>(row) * hidden + warp * kRotGroup + lane * 8) =
         make_uint2(packed[0], packed[1]);
@@ -90,7 +106,6 @@ convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride,
 // ---------------------------------------------------------------------------
 
 constexpr int kGemmM = 128, kGemmN = 256, kGemmK = 128;  // K in bytes == int8 elements
-constexpr int kGemmStages = 4;
 // warps 0-3: epilogue of the tile's first 128 columns, 4: TMA, 5: MMA, 6-7: idle,
 // 8-11: epilogue of the second 128 columns (a warp may only touch the TMEM lanes
 // 32*(warp%4)..: two warps per lane quarter halve the epilogue's time, which
@@ -98,18 +113,42 @@ constexpr int kGemmStages = 4;
 constexpr int kGemmThreads = 384;
 constexpr uint32_t kGemmABytes = kGemmM * kGemmK;  // 16384
 constexpr uint32_t kGemmBBytes = kGemmN * kGemmK;  // 32768
-constexpr uint32_t kGemmOffB = kGemmStages * kGemmABytes;
-constexpr uint32_t kGemmOffBar = kGemmOffB + kGemmStages * kGemmBBytes;
-constexpr uint32_t kGemmSmemBytes = kGemmOffBar + 256 + 1024;
 constexpr uint32_t kGemmTmemCols = 512;
 
-enum GemmAbort { kGemmAbortFull = 21, kGemmAbortEmpty, kGemmAbortAccFull, kGemmAbortAccEmpty };
+// What the eight 16-thread row slots of one 128-column half of a tile tell each
+// other in the carrier epilogue: per-warp largest magnitudes and per-slot
+// per-channel partial sums (maxima for V) of the rows 0-63 and 64-127 of the tile.
+struct EpilogueExchange {
+  float amax[2][4];                 // [row half][warp]
+  float column[2][8][H3S_HEAD_DIM];  // [row half][slot][channel]
+};
+constexpr uint32_t kEpilogueTileBytes = kGemmM * H3S_HEAD_DIM * 2;  // one half tile as bf16: 32 KB
+
+// Shared-memory layout.  The carrier epilogue stages each half tile as bf16 so
+// that it can be re-read column-wise (quantisation, statistics and every global
+// store then run on contiguous lines); it pays for the two 32 KB staging tiles
+// with one stage of the operand ring.
+template <bool kCarriers>
+struct GemmLayout {
+  static constexpr int kStages = kCarriers ? 3 : 4;
+  static constexpr uint32_t kOffB = kStages * kGemmABytes;
+  static constexpr uint32_t kOffTile = kOffB + kStages * kGemmBBytes;
+  static constexpr uint32_t kOffExchange = kOffTile + (kCarriers ? 2 * kEpilogueTileBytes : 0);
+  static constexpr uint32_t kOffBar = kOffExchange + (kCarriers ? 2 * sizeof(EpilogueExchange) : 0);
+  static constexpr uint32_t kBytes = kOffBar + 256 + 1024;
+  static_assert(kBytes <= 227 * 1024, "GEMM shared memory exceeds the per-CTA limit");
+};
+constexpr int kGemmMaxStages = 4;
+
+enum GemmAbort { kGemmAbortFull = 21, kGemmAbortEmpty, kGemmAbortAccFull, kGemmAbortAccEmpty, kGemmAbortTile, kGemmAbortExchange };
 
 struct GemmShared {
-  uint64_t full[kGemmStages];
-  uint64_t empty[kGemmStages];
+  uint64_t full[kGemmMaxStages];
+  uint64_t empty[kGemmMaxStages];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t tile_ready[2];      // per tile half: its four warps have staged their rows
+  uint64_t exchange_ready[2];  // per tile half: its four warps have written their EpilogueExchange
   uint32_t tmem_base;
   int abort_word;
 };
@@ -122,6 +161,11 @@ struct GemmParams {
   int32_t *status;
   int rows, n_out, hidden;
   int m_tiles, n_tiles;
+  // Column tiles are visited in the order (i * n_step) % n_tiles (n_step coprime with
+  // n_tiles, about a third of it): weight rows are ordered [Q | K | V], so consecutive
+  // tiles of a CTA alternate between the three kinds and the costlier epilogues of
+  // one kind spread out instead of arriving in a row.
+  int n_step;
   // optional per-head RMS norm (+ split-half rotation) of the Q and K groups
   const float *q_norm;    // (128) or null: no norm, no rotation
   const float *k_norm;    // (128)
@@ -131,6 +175,14 @@ struct GemmParams {
   int heads;
   float epsilon;
   unsigned long long wait_budget_ns;  // bound of every mbarrier wait
+  // carrier epilogue (h3s_qkv_gemm_chunk_carriers); all tensors cover the whole sequence
+  int8_t *q8, *k8;                 // (heads, sequence_total, 128); k8 null: K is staged
+  float *q_scale, *k_scale;        // (heads, ceil(S/128)), (heads, ceil(S/64))
+  void *q_summary, *k_summary;     // (heads, blocks, 128) tile means, summary_dtype
+  __nv_bfloat16 *k_stage, *v_stage;  // (heads, sequence_total, 128)
+  double *k_sum;                   // (heads, 128) running column sums of K, or null
+  unsigned int *v_amax_bits;       // (heads, 128) running column maxima of |V| as float bits
+  int summary_dtype, sequence_total, row_start;
 };
 
 __device__ __forceinline__ float rope_load(const void *base, int64_t index, int dtype) {
@@ -146,6 +198,37 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 }
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+__device__ __forceinline__ void store_summary(void *base, int dtype, int64_t at, double value) {
+  switch (dtype) {
+    case H3S_F64: static_cast<double *>(base)[at] = value; break;
+    case H3S_F32: static_cast<float *>(base)[at] = static_cast<float>(value); break;
+    case H3S_BF16: static_cast<__nv_bfloat16 *>(base)[at] = __float2bfloat16_rn(static_cast<float>(value)); break;
+    default: static_cast<__half *>(base)[at] = __float2half_rn(static_cast<float>(value)); break;
+  }
+}
+
+// INT8 codes of eight consecutive channels held as four bf16 pairs:
+// code = trunc(v/scale +- 0.5) with the correctly rounded quotient (the arithmetic
+// of quant_qk_blocks_kernel), written as one 8-byte store.
+template <bool kExact>
+__device__ __forceinline__ void quantise8(const uint4 &raw, const SharedDivisor &by_scale, int8_t *dst) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t code[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float q = divide<kExact>(by_scale, (i & 1) ? bf16_hi(w[i >> 1]) : bf16_lo(w[i >> 1]));
+    const float half_ulp = __uint_as_float((__float_as_uint(q) & 0x80000000u) | 0x3f000000u);  // +-0.5
+    q = __fadd_rn(q, half_ulp);
+    code[i] = static_cast<uint32_t>(static_cast<int>(q));  // truncation toward zero
+  }
+  uint32_t packed[2];
+#pragma unroll
+  for (int k = 0; k < 2; ++k)
+    packed[k] = __byte_perm(__byte_perm(code[4 * k], code[4 * k + 1], 0x0040),
+                            __byte_perm(code[4 * k + 2], code[4 * k + 3], 0x0040), 0x5410);
+  *reinterpret_cast<uint2 *>(dst) = make_uint2(packed[0], packed[1]);
+}
 
 // One row of one Q or K head after the GEMM, held as 64 bf16 pairs (every
 // intermediate of the reference epilogue is rounded to bf16, so the packed
@@ -213,26 +296,30 @@ __device__ __forceinline__ void norm_rope_row(uint32_t (&y)[H3S_HEAD_DIM / 2], c
   }
 }
 
+template <bool kCarriers>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const GemmParams prm) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
-  GemmShared &sh = *reinterpret_cast<GemmShared *>(smem + kGemmOffBar);
+  using L = GemmLayout<kCarriers>;
+  GemmShared &sh = *reinterpret_cast<GemmShared *>(smem + L::kOffBar);
   volatile int *abort_word = &sh.abort_word;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int k_steps = prm.hidden / kGemmK;
   const int total_tiles = prm.m_tiles * prm.n_tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kGemmStages; ++i) {
+    for (int i = 0; i < L::kStages; ++i) {
       ptx::mbar_init(&sh.full[i], 1);
       ptx::mbar_init(&sh.empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(&sh.acc_full[i], 1);
       ptx::mbar_init(&sh.acc_empty[i], 8);
+      ptx::mbar_init(&sh.tile_ready[i], 4);
+      ptx::mbar_init(&sh.exchange_ready[i], 4);
     }
     sh.abort_word = 0;
     ptx::fence_mbar_init();
@@ -253,14 +340,14 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const int tm = tile % prm.m_tiles, tn = tile / prm.m_tiles;
+        const int tm = tile % prm.m_tiles, tn = (tile / prm.m_tiles) * prm.n_step % prm.n_tiles;
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kGemmStages;
-          const uint32_t use = it / kGemmStages;
+          const int s = it % L::kStages;
+          const uint32_t use = it / L::kStages;
           if (!ptx::mbar_wait(&sh.empty[s], (use & 1u) ^ 1u, abort_word, kGemmAbortEmpty, prm.wait_budget_ns)) { ok = false; break; }
           ptx::mbar_arrive_expect_tx(&sh.full[s], kGemmABytes + kGemmBBytes);
           ptx::tma_load_2d(smem + s * kGemmABytes, &map_a, &sh.full[s], ks * kGemmK, tm * kGemmM);
-          ptx::tma_load_2d(smem + kGemmOffB + s * kGemmBBytes, &map_b, &sh.full[s], ks * kGemmK, tn * kGemmN);
+          ptx::tma_load_2d(smem + L::kOffB + s * kGemmBBytes, &map_b, &sh.full[s], ks * kGemmK, tn * kGemmN);
         }
       }
     }
@@ -275,13 +362,13 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         if (!ptx::mbar_wait(&sh.acc_empty[a], (acc_use & 1u) ^ 1u, abort_word, kGemmAbortAccEmpty, prm.wait_budget_ns)) { ok = false; break; }
         ptx::tc_fence_after();
         for (int ks = 0; ks < k_steps; ++ks, ++it) {
-          const int s = it % kGemmStages;
-          const uint32_t use = it / kGemmStages;
+          const int s = it % L::kStages;
+          const uint32_t use = it / L::kStages;
           if (!ptx::mbar_wait(&sh.full[s], use & 1u, abort_word, kGemmAbortFull, prm.wait_budget_ns)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint64_t a_desc = ptx::umma_desc_kmajor(ptx::smem_u32(smem + s * kGemmABytes), 1024, ptx::kSwizzle128);
           const uint64_t b_desc =
-              ptx::umma_desc_kmajor(ptx::smem_u32(smem + kGemmOffB + s * kGemmBBytes), 1024, ptx::kSwizzle128);
+              ptx::umma_desc_kmajor(ptx::smem_u32(smem + L::kOffB + s * kGemmBBytes), 1024, ptx::kSwizzle128);
 #pragma unroll
           for (int k = 0; k < kGemmK / 32; ++k)
             ptx::umma_i8(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
@@ -296,9 +383,10 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int gi = warp >= 8 ? 1 : 0;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t local = 0;
+    uint32_t exchanges = 0;  // uses of this half's exchange buffer and barrier so far
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
-      const int tm = tile % prm.m_tiles, tn = tile / prm.m_tiles;
+      const int tm = tile % prm.m_tiles, tn = (tile / prm.m_tiles) * prm.n_step % prm.n_tiles;
       const int a = local & 1;
       const uint32_t acc_use = local >> 1;
       {
@@ -314,6 +402,211 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int group = group_col0 >> 7;  // 128-column group == (kind, head)
         const bool group_ok = group_col0 < prm.n_out;
         const bool normed = prm.q_norm != nullptr && group < 2 * prm.heads;
+        if (kCarriers) {
+          // ---- carriers straight from the accumulators ----
+          // Phase A, one thread per row: de-quantise the row of this head to bf16
+          // (+ norm and rotation) and stage it in shared memory, 16-byte chunk c of
+          // row r at chunk position c ^ (r & 15) so that neither these row-wise
+          // writes nor the column-wise reads of phase B collide on banks.
+          unsigned char *tile = smem + L::kOffTile + gi * kEpilogueTileBytes;
+          const int local_row = quarter * 32 + lane;
+          {
+            uint32_t y[H3S_HEAD_DIM / 2];
+#pragma unroll
+            for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+              uint32_t acc[32];
+              H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + gi * H3S_HEAD_DIM + cc * 32, acc);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; i += 2) {
+                const float2 ws = group_ok ? __ldg(reinterpret_cast<const float2 *>(prm.w_scale + group_col0 + cc * 32 + i))
+                                           : make_float2(0.f, 0.f);
+                y[cc * 16 + (i >> 1)] =
+                    pack_bf16x2(__fmul_rn(static_cast<float>(static_cast<int>(acc[i])), __fmul_rn(xs, ws.x)),
+                                __fmul_rn(static_cast<float>(static_cast<int>(acc[i + 1])), __fmul_rn(xs, ws.y)));
+              }
+            }
+            // the accumulator is in registers: the MMA warp may refill it
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&sh.acc_empty[a]);
+            if (!group_ok) continue;  // the same for the four warps of this half
+            if (normed && row_ok) {
+              const void *rope_row = nullptr;
+              if (prm.rope != nullptr) {
+                const int64_t offset = static_cast<int64_t>(row) * prm.rope_stride_seq;
+                rope_row = prm.rope_dtype == H3S_F32
+                               ? static_cast<const void *>(static_cast<const float *>(prm.rope) + offset)
+                               : static_cast<const void *>(static_cast<const __nv_bfloat16 *>(prm.rope) + offset);
+              }
+              norm_rope_row(y, group < prm.heads ? prm.q_norm : prm.k_norm, prm.epsilon, rope_row, prm.rope_dtype,
+                            prm.rope_stride_dim, prm.rope_stride_rot, prm.rope_stride_pair);
+            }
+            uint4 *my_row = reinterpret_cast<uint4 *>(tile + local_row * (H3S_HEAD_DIM * 2));
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+              my_row[c ^ (local_row & 15)] = row_ok ? make_uint4(y[4 * c], y[4 * c + 1], y[4 * c + 2], y[4 * c + 3])
+                                                    : make_uint4(0u, 0u, 0u, 0u);  // rows past the chunk count as zeros
+          }
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&sh.tile_ready[gi]);
+          {
+            const bool got = ptx::mbar_wait(&sh.tile_ready[gi], exchanges & 1u, abort_word, kGemmAbortTile,
+                                            prm.wait_budget_ns);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+          }
+          // Phase B, 16 threads per row, 8 channels each: thread (slot, c) holds rows
+          // slot, slot+8, ... slot+120 of channels 8c..8c+7, as in quant_qk_blocks_kernel.
+          const int kind = group / prm.heads, head = group - kind * prm.heads;
+          const int g = quarter * 32 + lane;  // thread within this half's 128
+          const int slot = g >> 4, c = g & 15;
+          const bool quantise_here = kind == 0 || (kind == 1 && prm.k8 != nullptr);
+          EpilogueExchange &ex = reinterpret_cast<EpilogueExchange *>(smem + L::kOffExchange)[gi];
+          uint4 raw[16];
+#pragma unroll
+          for (int p = 0; p < 16; ++p) {
+            const int r = p * 8 + slot;
+            raw[p] = *reinterpret_cast<const uint4 *>(tile + r * (H3S_HEAD_DIM * 2) + ((c ^ (r & 15)) << 4));
+          }
+          {
+            // partial statistics of rows 0-63 (passes 0-7) and 64-127 (passes 8-15)
+            float part[2][8];
+            __nv_bfloat162 top[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              top[h] = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) part[h][i] = 0.f;
+#pragma unroll
+              for (int p = 8 * h; p < 8 * h + 8; ++p) {
+                const uint32_t w[4] = {raw[p].x, raw[p].y, raw[p].z, raw[p].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  if (kind == 2) {
+                    part[h][2 * i] = fmaxf(part[h][2 * i], fabsf(bf16_lo(w[i])));
+                    part[h][2 * i + 1] = fmaxf(part[h][2 * i + 1], fabsf(bf16_hi(w[i])));
+                  } else {
+                    part[h][2 * i] = __fadd_rn(part[h][2 * i], bf16_lo(w[i]));
+                    part[h][2 * i + 1] = __fadd_rn(part[h][2 * i + 1], bf16_hi(w[i]));
+                    if (quantise_here) {  // magnitudes two at a time: clear both sign bits, packed bf16 maximum
+                      const uint32_t magnitude = w[i] & 0x7fff7fffu;
+                      top[h] = __hmax2(top[h], *reinterpret_cast<const __nv_bfloat162 *>(&magnitude));
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) ex.column[h][slot][c * 8 + i] = part[h][i];
+              if (quantise_here) {
+                const uint32_t bits = *reinterpret_cast<const uint32_t *>(&top[h]);
+                const float amax = warp_max(fmaxf(bf16_lo(bits), bf16_hi(bits)));
+                if (lane == 0) ex.amax[h][quarter] = amax;
+              }
+            }
+          }
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&sh.exchange_ready[gi]);
+          {
+            const bool got = ptx::mbar_wait(&sh.exchange_ready[gi], exchanges & 1u, abort_word, kGemmAbortExchange,
+                                            prm.wait_budget_ns);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            ++exchanges;
+          }
+          // every thread of this half now holds its share of the tile in registers: the
+          // staging tile may be overwritten, the exchange block is read below
+          const int tile_row0 = prm.row_start + tm * kGemmM;  // first row of this tile within the sequence
+          const int valid = min(kGemmM, prm.rows - tm * kGemmM);
+          const int valid_half[2] = {min(H3S_KV_TILE, valid), max(0, valid - H3S_KV_TILE)};
+          float amax_half[2] = {0.f, 0.f};
+          if (quantise_here) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+              amax_half[h] = fmaxf(fmaxf(ex.amax[h][0], ex.amax[h][1]), fmaxf(ex.amax[h][2], ex.amax[h][3]));
+          }
+          // channel g of this head: totals over the eight row slots
+          double total[2] = {0.0, 0.0};
+          float peak = 0.f;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int sl = 0; sl < 8; ++sl) {
+              if (kind == 2) peak = fmaxf(peak, ex.column[h][sl][g]);
+              else total[h] += static_cast<double>(ex.column[h][sl][g]);
+            }
+          }
+          if (kind == 0) {
+            const int blocks_total = (prm.sequence_total + H3S_Q_TILE - 1) / H3S_Q_TILE;
+            const int block = tile_row0 / H3S_Q_TILE;
+            const float scale = __fadd_rn(__fdiv_rn(fmaxf(amax_half[0], amax_half[1]), 127.0f), 1.0e-7f);
+            if (g == 0) prm.q_scale[head * blocks_total + block] = scale;
+            store_summary(prm.q_summary, prm.summary_dtype,
+                          (static_cast<int64_t>(head) * blocks_total + block) * H3S_HEAD_DIM + g, (total[0] + total[1]) / valid);
+            int8_t *dst = prm.q8 + (static_cast<int64_t>(head) * prm.sequence_total + tile_row0) * H3S_HEAD_DIM + c * 8;
+            const SharedDivisor by_scale = make_divisor(scale);
+            if (by_scale.exact) {
+#pragma unroll
+              for (int p = 0; p < 16; ++p) {
+                const int r = p * 8 + slot;
+                if (r < valid) quantise8<true>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
+              }
+            } else {
+#pragma unroll 1
+              for (int p = 0; p < 16; ++p) {
+                const int r = p * 8 + slot;
+                if (r < valid) quantise8<false>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
+              }
+            }
+          } else if (kind == 1) {
+            const int blocks_total = (prm.sequence_total + H3S_KV_TILE - 1) / H3S_KV_TILE;
+            const int block0 = tile_row0 / H3S_KV_TILE;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (valid_half[h] > 0)
+                store_summary(prm.k_summary, prm.summary_dtype,
+                              (static_cast<int64_t>(head) * blocks_total + block0 + h) * H3S_HEAD_DIM + g, total[h] / valid_half[h]);
+            }
+            if (prm.k_sum != nullptr) atomicAdd(prm.k_sum + head * H3S_HEAD_DIM + g, total[0] + total[1]);
+            if (prm.k8 != nullptr) {
+              int8_t *dst = prm.k8 + (static_cast<int64_t>(head) * prm.sequence_total + tile_row0) * H3S_HEAD_DIM + c * 8;
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float scale = __fadd_rn(__fdiv_rn(amax_half[h], 127.0f), 1.0e-7f);
+                if (g == 0 && valid_half[h] > 0) prm.k_scale[head * blocks_total + block0 + h] = scale;
+                const SharedDivisor by_scale = make_divisor(scale);
+                if (by_scale.exact) {
+#pragma unroll
+                  for (int p = 8 * h; p < 8 * h + 8; ++p) {
+                    const int r = p * 8 + slot;
+                    if (r < valid) quantise8<true>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
+                  }
+                } else {
+#pragma unroll 1
+                  for (int p = 8 * h; p < 8 * h + 8; ++p) {
+                    const int r = p * 8 + slot;
+                    if (r < valid) quantise8<false>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
+                  }
+                }
+              }
+            } else {
+              __nv_bfloat16 *dst = prm.k_stage + (static_cast<int64_t>(head) * prm.sequence_total + tile_row0) * H3S_HEAD_DIM + c * 8;
+#pragma unroll
+              for (int p = 0; p < 16; ++p) {
+                const int r = p * 8 + slot;
+                if (r < valid) *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) = raw[p];
+              }
+            }
+          } else {
+            // non-negative floats order like their bit patterns
+            atomicMax(prm.v_amax_bits + head * H3S_HEAD_DIM + g, __float_as_uint(peak));
+            __nv_bfloat16 *dst = prm.v_stage + (static_cast<int64_t>(head) * prm.sequence_total + tile_row0) * H3S_HEAD_DIM + c * 8;
+#pragma unroll
+            for (int p = 0; p < 16; ++p) {
+              const int r = p * 8 + slot;
+              if (r < valid) *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) = raw[p];
+            }
+          }
+          continue;  // acc_empty was signalled above
+        }
         if (!normed) {
 #pragma unroll 1
           for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
@@ -433,15 +726,34 @@ static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const i
                                int rows, int hidden, int n_out, void *out_bf16, int64_t out_stride_head,
                                const float *q_norm, const float *k_norm, float epsilon, const void *rope,
                                int rope_dtype, const int64_t *rope_strides, int heads, int32_t *status,
-                               h3s_stream_t stream, const char *who) {
+                               h3s_stream_t stream, const char *who, const h3s_qkv_carriers *carriers = nullptr) {
   using namespace h3s;
-  H3S_CHECK_ARG(x_i8 && x_scale && w_i8 && w_scale && out_bf16, "%s: NULL pointer", who);
+  H3S_CHECK_ARG(x_i8 && x_scale && w_i8 && w_scale && (out_bf16 || carriers), "%s: NULL pointer", who);
   H3S_CHECK_ARG(rows > 0 && hidden > 0 && hidden % kGemmK == 0, "%s: hidden %d must be a positive multiple of 128", who, hidden);
   H3S_CHECK_ARG(n_out > 0 && n_out % H3S_HEAD_DIM == 0, "%s: n_out %d must be a multiple of 128", who, n_out);
-  H3S_CHECK_ARG(out_stride_head >= static_cast<int64_t>(rows) * H3S_HEAD_DIM && out_stride_head % 8 == 0,
+  H3S_CHECK_ARG(carriers != nullptr ||
+                    (out_stride_head >= static_cast<int64_t>(rows) * H3S_HEAD_DIM && out_stride_head % 8 == 0),
                 "%s: out_stride_head %lld is smaller than rows*128", who, static_cast<long long>(out_stride_head));
   H3S_CHECK_ARG(((reinterpret_cast<uintptr_t>(x_i8) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
                 "%s: operands must be 16-byte aligned", who);
+  if (carriers != nullptr) {
+    const h3s_qkv_carriers &c = *carriers;
+    H3S_CHECK_ARG(heads > 0 && n_out == 3 * heads * H3S_HEAD_DIM, "%s: n_out %d is not 3*heads*128 for %d heads", who, n_out, heads);
+    H3S_CHECK_ARG(c.q8 && c.q_scale && c.q_summary && c.k_summary && c.v_stage && c.stats,
+                  "%s: q8, q_scale, q_summary, k_summary, v_stage and stats are required", who);
+    H3S_CHECK_ARG((c.k8 != nullptr) == (c.k_scale != nullptr) && (c.k8 != nullptr) != (c.k_stage != nullptr),
+                  "%s: give either k8 + k_scale (K quantised per chunk) or k_stage (K staged for smoothing)", who);
+    H3S_CHECK_ARG(c.summary_dtype >= H3S_F32 && c.summary_dtype <= H3S_F64, "%s: bad summary dtype %d", who, c.summary_dtype);
+    H3S_CHECK_ARG(c.row_start >= 0 && c.row_start % H3S_Q_TILE == 0 && c.row_start + rows <= c.sequence_total,
+                  "%s: chunk [%d,%d) must start on a multiple of 128 inside the sequence of %d", who, c.row_start,
+                  c.row_start + rows, c.sequence_total);
+    H3S_CHECK_ARG(rows % H3S_Q_TILE == 0 || c.row_start + rows == c.sequence_total,
+                  "%s: only the final chunk may contain a partial tile", who);
+    const uintptr_t all = reinterpret_cast<uintptr_t>(c.q8) | reinterpret_cast<uintptr_t>(c.k8) |
+                          reinterpret_cast<uintptr_t>(c.k_stage) | reinterpret_cast<uintptr_t>(c.v_stage);
+    H3S_CHECK_ARG((all & 15) == 0 && (reinterpret_cast<uintptr_t>(c.stats) & 7) == 0,
+                  "%s: carriers and staging must be 16-byte aligned, stats 8-byte aligned", who);
+  }
   if (q_norm != nullptr || k_norm != nullptr || rope != nullptr) {
     H3S_CHECK_ARG(q_norm != nullptr && k_norm != nullptr, "%s: both norm weights are needed", who);
     H3S_CHECK_ARG(heads > 0 && n_out == 3 * heads * H3S_HEAD_DIM, "%s: n_out %d is not 3*heads*128 for %d heads", who, n_out, heads);
@@ -464,19 +776,46 @@ static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const i
   prm.out_stride_head = out_stride_head; prm.status = status;
   prm.rows = rows; prm.n_out = n_out; prm.hidden = hidden;
   prm.m_tiles = ceil_div(rows, kGemmM); prm.n_tiles = ceil_div(n_out, kGemmN);
+  prm.n_step = 1;
+  if (carriers != nullptr) {
+    auto gcd = [](int a, int b) { while (b) { const int t = a % b; a = b; b = t; } return a; };
+    int step = prm.n_tiles / 3 + 1;
+    while (step > 1 && gcd(step, prm.n_tiles) != 1) --step;
+    prm.n_step = step;
+  }
   prm.q_norm = q_norm; prm.k_norm = k_norm; prm.rope = rope; prm.rope_dtype = rope_dtype;
   prm.rope_stride_seq = rope ? rope_strides[0] : 0; prm.rope_stride_dim = rope ? rope_strides[1] : 0;
   prm.rope_stride_rot = rope ? rope_strides[2] : 0; prm.rope_stride_pair = rope ? rope_strides[3] : 0;
   prm.heads = heads; prm.epsilon = epsilon;
   prm.wait_budget_ns = wait_budget_ns();
+  prm.q8 = prm.k8 = nullptr; prm.q_scale = prm.k_scale = nullptr; prm.q_summary = prm.k_summary = nullptr;
+  prm.k_stage = prm.v_stage = nullptr; prm.k_sum = nullptr; prm.v_amax_bits = nullptr;
+  prm.summary_dtype = H3S_F32; prm.sequence_total = rows; prm.row_start = 0;
+  if (carriers != nullptr) {
+    const h3s_qkv_carriers &c = *carriers;
+    prm.q8 = c.q8; prm.k8 = c.k8; prm.q_scale = c.q_scale; prm.k_scale = c.k_scale;
+    prm.q_summary = c.q_summary; prm.k_summary = c.k_summary;
+    prm.k_stage = static_cast<__nv_bfloat16 *>(c.k_stage); prm.v_stage = static_cast<__nv_bfloat16 *>(c.v_stage);
+    // statistics scratch: double k_sum[heads*128]; uint32 v_amax_bits[heads*128] (the layout of h3s_column_stats)
+    double *sums = static_cast<double *>(c.stats);
+    prm.k_sum = c.k_stage != nullptr ? sums : nullptr;
+    prm.v_amax_bits = reinterpret_cast<unsigned int *>(sums + heads * H3S_HEAD_DIM);
+    prm.summary_dtype = c.summary_dtype; prm.sequence_total = c.sequence_total; prm.row_start = c.row_start;
+  }
   int device = 0, sms = 0;
   H3S_CHECK_CUDA(cudaGetDevice(&device));
   H3S_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(kGemmSmemBytes)));
   const int tiles = prm.m_tiles * prm.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
-  qkv_gemm_kernel<<<grid, kGemmThreads, kGemmSmemBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+  if (carriers != nullptr) {
+    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(GemmLayout<true>::kBytes)));
+    qkv_gemm_kernel<true><<<grid, kGemmThreads, GemmLayout<true>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+  } else {
+    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(GemmLayout<false>::kBytes)));
+    qkv_gemm_kernel<false><<<grid, kGemmThreads, GemmLayout<false>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+  }
   H3S_CHECK_CUDA(cudaGetLastError());
   return H3S_OK;
 }
@@ -497,6 +836,17 @@ int h3s_qkv_gemm_chunk_norm_rope(const int8_t *x_i8, const float *x_scale, const
   return qkv_gemm_chunk_impl(x_i8, x_scale, w_i8, w_scale, rows, hidden, 3 * heads * H3S_HEAD_DIM, out_bf16,
                              out_stride_head, q_norm, k_norm, epsilon, rope, rope_dtype, rope_strides, heads, status,
                              stream, "qkv_gemm_chunk_norm_rope");
+}
+
+int h3s_qkv_gemm_chunk_carriers(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8,
+                                const float *w_scale, int rows, int hidden, int heads,
+                                const h3s_qkv_carriers *carriers, const float *q_norm, const float *k_norm,
+                                float epsilon, const void *rope, int rope_dtype, const int64_t *rope_strides,
+                                int32_t *status, h3s_stream_t stream) {
+  H3S_CHECK_ARG(carriers != nullptr, "qkv_gemm_chunk_carriers: NULL carrier description");
+  return qkv_gemm_chunk_impl(x_i8, x_scale, w_i8, w_scale, rows, hidden, 3 * heads * H3S_HEAD_DIM, nullptr, 0, q_norm,
+                             k_norm, epsilon, rope, rope_dtype, rope_strides, heads, status, stream,
+                             "qkv_gemm_chunk_carriers", carriers);
 }
 
 }  // extern "C"

@@ -5,6 +5,7 @@
 // 128-channel row as 16-byte vectors (8 channels each), so a warp covers two
 // full rows and every global load/store is a fully used 128/256/512-byte line.
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 
@@ -167,31 +168,36 @@ quant_qk_blocks_kernel(const T *__restrict__ x, int64_t stride_h, int64_t stride
 
   int8_t *dst = out + (static_cast<int64_t>(head) * sequence_total + row_start + first_row) *
                           H3S_HEAD_DIM + c0;
+  // code = trunc(v/scale +- 0.5): the half carries the quotient's sign bit, the four
+  // codes of a word are gathered with byte permutes.  The divisor's exactness is
+  // tested once, around the whole loop (see divide<>).
+  auto emit = [&](auto exact_tag) {
+    constexpr bool kExact = decltype(exact_tag)::value;
 #pragma unroll
-  for (int p = 0; p < kPasses; ++p) {
-    const int r = p * kSlots + slot;
-    if (out != nullptr && r < valid_rows) {
-      float v[8];
-      Elem<T>::unpack(raw[p], v);
-      // code = trunc(v/scale +- 0.5): the half carries the quotient's sign bit,
-      // the four codes of a word are gathered with byte permutes
-      uint32_t code[8];
+    for (int p = 0; p < kPasses; ++p) {
+      const int r = p * kSlots + slot;
+      if (out != nullptr && r < valid_rows) {
+        float v[8];
+        Elem<T>::unpack(raw[p], v);
+        uint32_t code[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float q = divide(by_scale, kHasMean ? __fsub_rn(v[i], mu[i]) : v[i]);
-        const float half = __uint_as_float((__float_as_uint(q) & 0x80000000u) | 0x3f000000u);
-        q = __fadd_rn(q, half);
-        code[i] = static_cast<uint32_t>(static_cast<int>(q));  // truncation toward zero
+        for (int i = 0; i < 8; ++i) {
+          float q = divide<kExact>(by_scale, kHasMean ? __fsub_rn(v[i], mu[i]) : v[i]);
+          const float half = __uint_as_float((__float_as_uint(q) & 0x80000000u) | 0x3f000000u);
+          q = __fadd_rn(q, half);
+          code[i] = static_cast<uint32_t>(static_cast<int>(q));  // truncation toward zero
+        }
+        uint32_t packed[2];
+#pragma unroll
+        for (int w = 0; w < 2; ++w)
+          packed[w] = __byte_perm(__byte_perm(code[4 * w], code[4 * w + 1], 0x0040),
+                                  __byte_perm(code[4 * w + 2], code[4 * w + 3], 0x0040), 0x5410);
+        *reinterpret_cast<uint2 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) =
+            make_uint2(packed[0], packed[1]);
       }
-      uint32_t packed[2];
-#pragma unroll
-      for (int w = 0; w < 2; ++w)
-        packed[w] = __byte_perm(__byte_perm(code[4 * w], code[4 * w + 1], 0x0040),
-                                __byte_perm(code[4 * w + 2], code[4 * w + 3], 0x0040), 0x5410);
-      *reinterpret_cast<uint2 *>(dst + static_cast<int64_t>(r) * H3S_HEAD_DIM) =
-          make_uint2(packed[0], packed[1]);
     }
-  }
+  };
+  if (by_scale.exact) emit(std::true_type{}); else emit(std::false_type{});
 
   if (summary != nullptr && threadIdx.x < H3S_HEAD_DIM) {
     const int d = threadIdx.x;
@@ -254,6 +260,9 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
   }
 
   const T *base = v + head * stride_h + c0;
+  // the divisors' exactness is tested once, around the whole loop (see divide<>)
+  auto fill = [&](auto exact_tag) {
+  constexpr bool kExact = decltype(exact_tag)::value;
 #pragma unroll
   for (int p = 0; p < kVTile / (kVThreads / 16 * 4); ++p) {
     const int r0 = (p * (kVThreads / 16) + slot) * 4;  // four consecutive rows
@@ -267,7 +276,7 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
         Elem<T>::load8(base + static_cast<int64_t>(first_row + r0 + j) * stride_s, raw);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          if (all_exact) {  // shared-divisor division, see SharedDivisor
+          if (kExact) {  // shared-divisor division, see SharedDivisor
             const float q0 = __fmul_rn(raw[i], rc[i]);
             q[j][i] = __fmaf_rn(__fmaf_rn(-sc[i], q0, raw[i]), rc[i], q0);
           } else {
@@ -293,6 +302,8 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
     for (int i = 0; i < 8; ++i)
       *reinterpret_cast<uint32_t *>(&tile[v_tile_offset(c0 + i, r0)]) = word[i];
   }
+  };
+  if (all_exact) fill(std::true_type{}); else fill(std::false_type{});
   __syncthreads();
   uint8_t *dst = out + static_cast<int64_t>(head) * H3S_HEAD_DIM * padded_total + row_start + first_row;
 #pragma unroll
@@ -436,6 +447,27 @@ int h3s_column_stats(const void *k, int64_t k_stride_h, int64_t k_stride_s, cons
     case H3S_BF16: return launch_column_stats<__nv_bfloat16>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
     default: return launch_column_stats<__half>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
   }
+}
+
+int h3s_column_stats_finalize(const void *stats, int dtype, int heads, int sequence, float v_bound,
+                              float *k_mean, float *v_scale, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(stats != nullptr && (reinterpret_cast<uintptr_t>(stats) & 7) == 0, "column_stats_finalize: stats must be non-NULL and 8-byte aligned");
+  H3S_CHECK_ARG(heads > 0 && sequence > 0, "column_stats_finalize: empty problem");
+  H3S_CHECK_ARG(k_mean != nullptr || v_scale != nullptr, "column_stats_finalize: nothing to produce");
+  H3S_CHECK_ARG(v_scale == nullptr || v_bound > 0.f, "column_stats_finalize: v_bound must be positive");
+  H3S_CHECK_ARG(dtype == H3S_F32 || dtype == H3S_BF16 || dtype == H3S_F16, "column_stats_finalize: unsupported dtype %d", dtype);
+  const double *k_sum = static_cast<const double *>(stats);
+  const unsigned int *v_bits = reinterpret_cast<const unsigned int *>(k_sum + heads * H3S_HEAD_DIM);
+  const int total = heads * H3S_HEAD_DIM;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case H3S_F32: column_stats_finalize_kernel<float><<<ceil_div(total, 256), 256, 0, s>>>(k_sum, v_bits, total, sequence, v_bound, k_mean, v_scale); break;
+    case H3S_BF16: column_stats_finalize_kernel<__nv_bfloat16><<<ceil_div(total, 256), 256, 0, s>>>(k_sum, v_bits, total, sequence, v_bound, k_mean, v_scale); break;
+    default: column_stats_finalize_kernel<__half><<<ceil_div(total, 256), 256, 0, s>>>(k_sum, v_bits, total, sequence, v_bound, k_mean, v_scale); break;
+  }
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
 }
 
 int h3s_quant_qk_blocks(const void *x, int dtype, int64_t x_stride_h, int64_t x_stride_s,

@@ -268,6 +268,90 @@ def qkv_gemm_chunk(x_i8, x_scale, w_i8, w_scale, staging, *, row_start=0, status
     )
 
 
+def column_stats_scratch(heads, device):
+    """Zeroed statistics scratch (K column sums in FP64, V column maxima) for
+    ``qkv_gemm_chunk_carriers`` / ``column_stats_finalize``."""
+    lib = _native.load()
+    return torch.zeros(lib.h3s_column_stats_scratch_bytes(int(heads)), dtype=torch.uint8, device=device)
+
+
+def column_stats_finalize(stats, heads, sequence, *, want_k_mean, dtype=torch.bfloat16, v_bound=FP8_V_BOUND):
+    """``(k_mean | None, v_scale)`` from an accumulated statistics scratch."""
+    lib = _native.load()
+    k_mean = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=stats.device) if want_k_mean else None
+    v_scale = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=stats.device)
+    check(
+        lib.h3s_column_stats_finalize(ptr(stats), dtype_code(dtype), int(heads), int(sequence), float(v_bound),
+                                      ptr(k_mean), ptr(v_scale), stream_ptr(stats.device)),
+        "h3s_column_stats_finalize",
+    )
+    return k_mean, v_scale
+
+
+def qkv_gemm_chunk_carriers(x_i8, x_scale, w_i8, w_scale, *, heads, row_start, q_int8, q_scale, q_summary,
+                            k_summary, v_stage, stats, k_int8=None, k_scale=None, k_stage=None, status=None,
+                            q_norm=None, k_norm=None, epsilon=1e-6, rope=None):
+    """INT8 GEMM of one chunk whose epilogue writes the carriers of rows
+    ``[row_start, row_start + rows)``: INT8 Q blocks + scales + tile means, K
+    either quantised the same way (``k_int8`` + ``k_scale``) or staged as bf16
+    (``k_stage``) with its column sums accumulated in ``stats``, V staged as
+    bf16 with its column maxima accumulated in ``stats``.  All output tensors
+    cover the whole sequence."""
+    lib = _native.load()
+    rows, hidden = x_i8.shape
+    sequence = q_int8.shape[2]
+    n_out = 3 * heads * HEAD_DIM
+    if (x_i8.dtype != torch.int8 or w_i8.dtype != torch.int8 or not x_i8.is_contiguous() or not w_i8.is_contiguous()
+            or tuple(w_i8.shape) != (n_out, hidden)):
+        raise _native.NativeError("qkv_gemm_chunk_carriers: operands must be contiguous int8, weight (3*heads*128, hidden)")
+    if x_scale.dtype != torch.float32 or w_scale.dtype != torch.float32 or x_scale.numel() < rows or w_scale.numel() != n_out:
+        raise _native.NativeError("qkv_gemm_chunk_carriers: scales must be fp32 (rows,) and (n_out,)")
+    q_blocks, k_blocks = _ceil_div(sequence, Q_TILE), _ceil_div(sequence, KV_TILE)
+    expect = [("q_int8", q_int8, (1, heads, sequence, HEAD_DIM), torch.int8),
+              ("q_scale", q_scale, (1, heads, q_blocks), torch.float32),
+              ("q_summary", q_summary, (1, heads, q_blocks, HEAD_DIM), None),
+              ("k_summary", k_summary, (1, heads, k_blocks, HEAD_DIM), q_summary.dtype),
+              ("v_stage", v_stage, (1, heads, sequence, HEAD_DIM), torch.bfloat16)]
+    if k_stage is not None:
+        expect.append(("k_stage", k_stage, (1, heads, sequence, HEAD_DIM), torch.bfloat16))
+        if k_int8 is not None or k_scale is not None:
+            raise _native.NativeError("qkv_gemm_chunk_carriers: K is either staged or quantised, not both")
+    else:
+        expect += [("k_int8", k_int8, (1, heads, sequence, HEAD_DIM), torch.int8),
+                   ("k_scale", k_scale, (1, heads, k_blocks), torch.float32)]
+    for name, t, shape, dt in expect:
+        if t is None or tuple(t.shape) != shape or (dt is not None and t.dtype != dt) or not t.is_contiguous() \
+                or t.device != x_i8.device:
+            raise _native.NativeError("qkv_gemm_chunk_carriers: %s must be a contiguous %s tensor of shape %s on the GEMM's device"
+                                      % (name, dt, shape))
+    carriers = _native.QKVCarriers(
+        q8=q_int8.data_ptr(), q_scale=q_scale.data_ptr(), q_summary=q_summary.data_ptr(),
+        k8=None if k_int8 is None else k_int8.data_ptr(), k_scale=None if k_scale is None else k_scale.data_ptr(),
+        k_summary=k_summary.data_ptr(), k_stage=None if k_stage is None else k_stage.data_ptr(),
+        v_stage=v_stage.data_ptr(), stats=stats.data_ptr(), summary_dtype=dtype_code(q_summary.dtype),
+        sequence_total=int(sequence), row_start=int(row_start),
+    )
+    if (q_norm is None) != (k_norm is None):
+        raise _native.NativeError("qkv_gemm_chunk_carriers: q_norm and k_norm go together")
+    if rope is not None and q_norm is None:
+        raise _native.NativeError("qkv_gemm_chunk_carriers: the rotation needs the norm weights")
+    rope_ptr, rope_code, strides = None, 0, None
+    if rope is not None:
+        if (rope.ndim != 6 or tuple(rope.shape[:3]) != (1, sequence, 1) or tuple(rope.shape[3:]) != (48, 2, 2)
+                or rope.device != x_i8.device or rope.dtype not in (torch.float32, torch.bfloat16)):
+            raise _native.NativeError("qkv_gemm_chunk_carriers: rope must be fp32/bf16 (1, %d, 1, 48, 2, 2) on the GEMM's device" % sequence)
+        rope_ptr = ctypes.c_void_p(rope.data_ptr() + int(row_start) * rope.stride(1) * rope.element_size())
+        rope_code = dtype_code(rope.dtype)
+        strides = (ctypes.c_int64 * 4)(rope.stride(1), rope.stride(3), rope.stride(4), rope.stride(5))
+    check(
+        lib.h3s_qkv_gemm_chunk_carriers(
+            ptr(x_i8), ptr(x_scale), ptr(w_i8), ptr(w_scale), rows, hidden, int(heads), ctypes.byref(carriers),
+            ptr(q_norm), ptr(k_norm), float(epsilon), rope_ptr, rope_code, strides, ptr(status),
+            stream_ptr(x_i8.device)),
+        "h3s_qkv_gemm_chunk_carriers",
+    )
+
+
 def route_topk(q_summary, k_summary, *, q_start, q_stop, kv_start, kv_stop, retained):
     """Compact route ``int32 (1,H,q_stop-q_start,route_len)``."""
     lib = _native.load()

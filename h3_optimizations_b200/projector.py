@@ -6,14 +6,18 @@ projected in 4096-row chunks straight into full-length quantised carriers, so
 no full-precision Q/K/V of the whole sequence is handed to the backend.
 
 Per chunk:  ConvRot (Hadamard-256) + per-row INT8 of the activations
-            -> tcgen05 INT8 GEMM against the INT8 QKV weight, de-quantised to
-               bf16 head-major staging
-            -> INT8 Q blocks (+ tile means) immediately.
+            -> tcgen05 INT8 GEMM against the INT8 QKV weight whose epilogue
+               writes the carriers: INT8 Q blocks, scales and tile means
+               straight from the accumulators (Q is never stored in a wider
+               format), K tile means, bf16 staging of K and V with their
+               column sums / maxima accumulated on the way.
 After the last chunk (K smoothing and the V scale need whole-sequence
-statistics): column statistics over the staged K and V, INT8 K blocks with the
-mean removed (+ tile means of the raw K), FP8-E4M3 V carrier.  With
+statistics): the statistics are finalised, the staged K is quantised with the
+mean removed and the staged V becomes the FP8-E4M3 carrier.  With
 ``smooth_k=False`` (what every chunked producer of the reference does,
-chunked_qkv.py:289) K is quantised per chunk as well.
+chunked_qkv.py:289) K leaves the epilogue as INT8 blocks like Q and only V is
+staged.  The default keeps the smoothing on, which is what the attention
+kernel's accuracy figures are stated for.
 
 The module handed to ``project`` must expose ``heads``, ``head_dim`` and the
 INT8 weight in the rotated domain: ``qkv_weight_int8`` (3*H*128, hidden) with
@@ -40,6 +44,16 @@ from .router import KV_TILE, Q_TILE
 CHUNK_ROWS = 4096
 HEAD_DIM = 128
 V_QUANT_BOUND = 448.0
+
+
+_SIDE_STREAMS = {}
+
+
+def _side_stream(device):
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _SIDE_STREAMS:
+        _SIDE_STREAMS[key] = torch.cuda.Stream(device)
+    return _SIDE_STREAMS[key]
 
 
 def _validate_chunk_rows(chunk_rows, q_tile=Q_TILE, kv_tile=KV_TILE):
@@ -144,27 +158,37 @@ def run_chunked_sparse_qkv(x, w_i8, w_scale, *, heads, head_dim=HEAD_DIM, layer_
         k_scale = torch.empty((1, heads, k_blocks), dtype=torch.float32, device=device)
         q_summary = torch.empty((1, heads, q_blocks, HEAD_DIM), dtype=summary_dtype, device=device)
         k_summary = torch.empty((1, heads, k_blocks, HEAD_DIM), dtype=summary_dtype, device=device)
-        # head-major bf16 staging of the projection, whole sequence (K and V need
-        # whole-sequence statistics before they can be quantised)
-        staging = torch.empty((3 * heads, sequence, HEAD_DIM), dtype=torch.bfloat16, device=device)
+        # bf16 staging of what needs whole-sequence statistics before it can be quantised
+        v_stage = torch.empty(shape, dtype=torch.bfloat16, device=device)
+        k_stage = torch.empty(shape, dtype=torch.bfloat16, device=device) if smooth_k else None
+        stats = ops.column_stats_scratch(heads, device)
         x_i8 = torch.empty((min(chunk_rows, sequence), hidden), dtype=torch.int8, device=device)
         x_scale = torch.empty((min(chunk_rows, sequence),), dtype=torch.float32, device=device)
-        q_stage = staging[:heads].unsqueeze(0)
-        k_stage = staging[heads:2 * heads].unsqueeze(0)
-        v_stage = staging[2 * heads:].unsqueeze(0)
         w_i8 = w_i8.contiguous()
         for start, end in chunk_ranges(sequence, chunk_rows):
             rows = end - start
             ops.convrot_quant_rows(x[start:end], x_i8, x_scale)
-            ops.qkv_gemm_chunk(x_i8[:rows], x_scale[:rows], w_i8, w_scale, staging, row_start=start, status=status,
-                               q_norm=q_norm, k_norm=k_norm, epsilon=epsilon, rope=rope_freqs)
-            ops.quant_qk_blocks_into(q_stage[:, :, start:end], q_int8, q_scale, q_summary, block=Q_TILE, row_start=start)
-            if not smooth_k:
-                ops.quant_qk_blocks_into(k_stage[:, :, start:end], k_int8, k_scale, k_summary, block=KV_TILE, row_start=start)
-        k_mean, v_scale = ops.column_stats(k_stage if smooth_k else None, v_stage, V_QUANT_BOUND)
+            ops.qkv_gemm_chunk_carriers(
+                x_i8[:rows], x_scale[:rows], w_i8, w_scale, heads=heads, row_start=start,
+                q_int8=q_int8, q_scale=q_scale, q_summary=q_summary, k_summary=k_summary, v_stage=v_stage,
+                stats=stats, k_int8=None if smooth_k else k_int8, k_scale=None if smooth_k else k_scale,
+                k_stage=k_stage, status=status, q_norm=q_norm, k_norm=k_norm, epsilon=epsilon, rope=rope_freqs)
+        k_mean, v_scale = ops.column_stats_finalize(stats, heads, sequence, want_k_mean=smooth_k,
+                                                    dtype=torch.bfloat16, v_bound=V_QUANT_BOUND)
+        v_carrier = ops.allocate_v_carrier(sequence, heads, device)
         if smooth_k:
-            ops.quant_qk_blocks_into(k_stage, k_int8, k_scale, k_summary, block=KV_TILE, mean=k_mean)
-        v_carrier, v_scale = ops.quant_v_fp8(v_stage, v_scale, V_QUANT_BOUND)
+            # the two second-phase quantisers are independent and each leaves part of the
+            # memory system idle: V runs on a second stream underneath K
+            main, side = torch.cuda.current_stream(device), _side_stream(device)
+            side.wait_stream(main)
+            try:
+                with torch.cuda.stream(side):
+                    ops.quant_v_fp8_into(v_stage, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
+                ops.quant_qk_blocks_into(k_stage, k_int8, k_scale, None, block=KV_TILE, mean=k_mean)
+            finally:
+                main.wait_stream(side)  # on every exit path, before the staging can be freed
+        else:
+            ops.quant_v_fp8_into(v_stage, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
     except _native.NativeError as exc:
         raise FusedQKVError("chunked QKV projection failed: layer=%d: %s" % (layer_index, exc)) from exc
     return validate_prepared_fused_qkv(

@@ -232,6 +232,70 @@ int h3s_route_to_delta_lut(const int32_t *route, int heads, int q_tiles,
                            h3s_stream_t stream);
 
 /*
+ * Carrier outputs of h3s_qkv_gemm_chunk_carriers.  Every tensor covers the
+ * WHOLE sequence of `sequence_total` rows (the chunk lands at row_start):
+ *   q8, k8        int8 (heads, sequence_total, 128)
+ *   q_scale       fp32 (heads, ceil(S/128));  k_scale fp32 (heads, ceil(S/64))
+ *   q_summary     (heads, ceil(S/128), 128), k_summary (heads, ceil(S/64), 128):
+ *                 tile means of the de-quantised (normed, rotated) Q and K,
+ *                 element type summary_dtype
+ *   k_stage, v_stage  bf16 (heads, sequence_total, 128)
+ *   stats         h3s_column_stats_scratch_bytes(heads) bytes, zeroed by the
+ *                 caller before the first chunk of a sequence
+ * K is either quantised per chunk like Q (k8 + k_scale given, k_stage NULL: no
+ * mean smoothing, what the reference's chunked producers do,
+ * attention/sparse/chunked_qkv.py:289) or staged in bf16 (k_stage given, k8 and
+ * k_scale NULL) while its column sums accumulate in `stats`, to be quantised
+ * with the whole-sequence mean removed once every chunk is through.  V is
+ * always staged while its column maxima accumulate in `stats`.
+ */
+typedef struct h3s_qkv_carriers {
+  int8_t *q8;
+  float *q_scale;
+  void *q_summary;
+  int8_t *k8;
+  float *k_scale;
+  void *k_summary;
+  void *k_stage;
+  void *v_stage;
+  void *stats;
+  int summary_dtype;
+  int sequence_total;
+  int row_start;
+} h3s_qkv_carriers;
+
+/*
+ * h3s_qkv_gemm_chunk[_norm_rope] whose epilogue emits carriers instead of bf16
+ * staging: per 128-row Q block of a head the block amax, scale = amax/127+1e-7,
+ * INT8 codes trunc(y/scale +- 0.5) and the tile mean; the same per 64-row K
+ * block when K is not smoothed (see h3s_qkv_carriers).  q_norm/k_norm/rope as
+ * in h3s_qkv_gemm_chunk_norm_rope, all three may be NULL.  rows must be a
+ * multiple of 128 except in the final chunk of the sequence.
+ * Replaces _fused_qk_kernel / _fused_v_kernel including their quantising
+ * epilogues (attention/sparse/fused_qkv.py:292-367,427-438) and the per-chunk
+ * packing of pack_sparse_qk_chunk_into (attention/sparse/chunked_qkv.py:119-203,247-273).
+ */
+int h3s_qkv_gemm_chunk_carriers(const int8_t *x_i8, const float *x_scale,
+                                const int8_t *w_i8, const float *w_scale,
+                                int rows, int hidden, int heads,
+                                const h3s_qkv_carriers *carriers,
+                                const float *q_norm, const float *k_norm,
+                                float epsilon, const void *rope, int rope_dtype,
+                                const int64_t *rope_strides, int32_t *status,
+                                h3s_stream_t stream);
+
+/*
+ * Second phase of the statistics that h3s_qkv_gemm_chunk_carriers accumulates
+ * (or any scratch in h3s_column_stats' layout): k_mean = sum/sequence rounded to
+ * `dtype` and widened, v_scale = max(amax/v_bound, 1e-20); either output may be
+ * NULL.  Replaces finalize_v_scale (attention/sparse/fp8_v_stream.py:58-66) and
+ * the mean of attention/sparse/sparse_sage.py:319.
+ */
+int h3s_column_stats_finalize(const void *stats, int dtype, int heads,
+                              int sequence, float v_bound, float *k_mean,
+                              float *v_scale, h3s_stream_t stream);
+
+/*
  * Upper bound, in nanoseconds, of every wait inside the tcgen05 kernels
  * (attention and QKV GEMM) launched after the call; default 2 s, accepted range
  * 1 us .. 60 s.  A wait that runs out ends the kernel with a code in the
