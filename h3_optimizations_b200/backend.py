@@ -331,9 +331,12 @@ class B200SparseBackend:
         )
         return PreparedHybrid(sparse=sparse)
 
-    def execute(self, prepared, out=None):
+    def execute(self, prepared, out=None, peer_out_ptrs=None):
         """Run the attention kernel on prepared carriers.  ``out`` (optional) is
-        an HND ``(1, H, S, 128)`` tensor or view to write into."""
+        an HND ``(1, H, S, 128)`` tensor or view to write into;
+        ``peer_out_ptrs`` (head-sharded runs, see ``sharding.HeadShardedBackend``)
+        are the device addresses of the same head slice inside the peers'
+        outputs, which receive every tile as well."""
         sparse = prepared.sparse
         route = sparse.route
         geometry = route.geometry
@@ -345,7 +348,7 @@ class B200SparseBackend:
                 sparse.q_int8, sparse.k_int8, sparse.v_carrier, sparse.q_scale, sparse.k_scale,
                 sparse.v_scale, route.indices,
                 q_start=geometry.pure_video_q_start, q_stop=geometry.pure_video_q_stop,
-                out=out, out_dtype=out_dtype, status=word,
+                out=out, out_dtype=out_dtype, status=word, peer_out_ptrs=peer_out_ptrs,
             )
             mirror.copy_(word, non_blocking=True)  # 16 bytes, stream ordered behind the kernel
             copied.record(torch.cuda.current_stream(device))

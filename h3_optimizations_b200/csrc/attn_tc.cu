@@ -481,10 +481,10 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
     if (ok) {
       // Epilogue: O * v_scale / l -> OutT, staged through shared memory (the K
       // stage ring is free: every TMA load has been consumed) so that each warp
-      // writes its 32 rows as full contiguous lines - to the local output and,
-      // in a head-sharded run, to the same slice of every peer GPU's output
-      // (plain stores over NVLink).  A warp only reads back the rows it staged
-      // itself, so __syncwarp is the only synchronisation.
+      // writes its 32 rows as full contiguous lines to the local output.  A
+      // warp only reads back the rows it staged itself, so __syncwarp is the
+      // only synchronisation.  In a head-sharded run the staged tile is also
+      // copied to the peers, by the whole CTA, after the teardown barrier.
       ptx::tc_fence_after();
       const float inv_l = 1.0f / l;
       constexpr int kRowBytes = H3S_HEAD_DIM * static_cast<int>(sizeof(OutT));
@@ -518,18 +518,16 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
       ptx::tc_fence_before();
       __syncwarp();
       const int warp_row0 = warp * 32;
-      for (int dest = 0; dest <= prm.n_peer_out; ++dest) {
-        unsigned char *base = static_cast<unsigned char *>(dest == 0 ? prm.out : prm.peer_out[dest - 1]);
+      unsigned char *base = static_cast<unsigned char *>(prm.out);
 #pragma unroll 4
-        for (int idx = lane; idx < 32 * kChunksPerRow; idx += 32) {
-          const int r = warp_row0 + idx / kChunksPerRow, c = idx % kChunksPerRow;
-          const int grow = tq * H3S_Q_TILE + r;
-          if (grow < prm.sequence) {
-            const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * kRowBytes + ((c ^ (r & 15)) << 4));
-            unsigned char *dst = base + (head * prm.out_stride_h + static_cast<int64_t>(grow) * prm.out_stride_s) *
-                                            static_cast<int64_t>(sizeof(OutT)) + c * 16;
-            *reinterpret_cast<uint4 *>(dst) = value;
-          }
+      for (int idx = lane; idx < 32 * kChunksPerRow; idx += 32) {
+        const int r = warp_row0 + idx / kChunksPerRow, c = idx % kChunksPerRow;
+        const int grow = tq * H3S_Q_TILE + r;
+        if (grow < prm.sequence) {
+          const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * kRowBytes + ((c ^ (r & 15)) << 4));
+          unsigned char *dst = base + (head * prm.out_stride_h + static_cast<int64_t>(grow) * prm.out_stride_s) *
+                                          static_cast<int64_t>(sizeof(OutT)) + c * 16;
+          *reinterpret_cast<uint4 *>(dst) = value;
         }
       }
     }
@@ -552,6 +550,29 @@ sparse_attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_co
   if (warp == 5) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  // Head-sharded run: the finished tile, still staged in shared memory, goes to
+  // the same slice of every peer GPU's output with plain stores over NVLink.
+  // All six warps share the copy (the producer and MMA warps have nothing left
+  // to do), and each 16-byte chunk is sent to all peers back to back, so the
+  // stores of one CTA are spread over every link at once instead of filling
+  // one destination after the other.
+  if (code == 0 && prm.n_peer_out > 0) {
+    constexpr int kRowBytes = H3S_HEAD_DIM * static_cast<int>(sizeof(OutT));
+    constexpr int kChunksPerRow = kRowBytes / 16;
+    const unsigned char *stage = smem + kOffK;
+    const int64_t tile_offset = head * prm.out_stride_h * static_cast<int64_t>(sizeof(OutT));
+    for (int idx = threadIdx.x; idx < H3S_Q_TILE * kChunksPerRow; idx += kAttnThreads) {
+      const int r = idx / kChunksPerRow, c = idx % kChunksPerRow;
+      const int grow = tq * H3S_Q_TILE + r;
+      if (grow < prm.sequence) {
+        const uint4 value = *reinterpret_cast<const uint4 *>(stage + r * kRowBytes + ((c ^ (r & 15)) << 4));
+        const int64_t at = tile_offset + static_cast<int64_t>(grow) * prm.out_stride_s * static_cast<int64_t>(sizeof(OutT)) + c * 16;
+#pragma unroll
+        for (int d = 0; d < H3S_MAX_PEER_OUTPUTS; ++d)
+          if (d < prm.n_peer_out) *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(prm.peer_out[d]) + at) = value;
+      }
+    }
   }
 }
 
