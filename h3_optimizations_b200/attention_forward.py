@@ -1,19 +1,24 @@
 """The attention-module transaction that calls the hot path.
 
-Mirror of the reference's ``make_forward`` (attention_forward.py:131-246): one
-closure per DiT block that replaces ``block.attn.forward``.  With a projector
-installed the activations go ``projector.project -> backend.prepare_projected
--> backend.execute[_projected] -> out_proj`` and never exist as floating-point
-Q/K/V; without one (or when the projector declines and no fallback was given)
-the module's own ``qkv_proj`` runs, Q and K get the RMS norm and the split-half
-rotation, and the HND views go through ``backend.prepare`` / ``execute``.
+Takes the place of the reference's ``make_forward`` (attention_forward.py:131-246):
+one replacement for ``block.attn.forward`` per DiT block.  The contract kept is
+the call signature ``forward(x, rope_freqs=None, transformer_options=None)``,
+the backend / projector protocols it drives, the marker attributes left on the
+returned function and the error texts.  The transaction itself is an object
+(``AttentionTransaction``) with one method per route through the block:
 
+* ``projected``: ``projector.[try_]project -> backend.prepare_projected ->
+  backend.execute_projected | execute -> out_proj``; the activations never
+  exist as floating-point Q/K/V;
+* ``unprojected``: the module's own ``qkv_proj``, RMS norm and split-half
+  rotation of Q and K, HND views through ``backend.prepare`` / ``execute``.
+
+A projector that declines (``try_project`` returns ``None``) hands the call to
+the fallback forward when one was given, else to the unprojected route.  The
+reference's dense ``attention=`` arm and its fallback to a dense kernel do not
+exist here (this package has exactly one backend), so ``backend`` is required.
 The module must expose ``qkv_proj, q_norm, k_norm, out_proj, heads, head_dim``
-(patch.py:13-20).  Control flow, argument names, the markers left on the
-closure and the error texts follow the reference; the reference's dense
-``attention=`` arm and its ``AttentionBackendUnavailable`` fallback to a dense
-kernel do not exist here (this package has exactly one backend and no dense
-path), so ``backend`` is required.
+(patch.py:13-20).
 """
 
 from __future__ import annotations
@@ -64,71 +69,81 @@ def project_qkv(module, x, rope_freqs):
 
 def to_hnd(q, k, v):
     """``(S, H, 128)`` -> HND ``(1, H, S, 128)`` strided views (attention_forward.py:55-60)."""
-    return (q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0), v.transpose(0, 1).unsqueeze(0))
+    return tuple(t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
 
 
-def _backend_name(backend):
-    return getattr(backend, "name", type(backend).__name__)
+class AttentionTransaction:
+    """One block's attention call.  Holds the module, its layer index, the
+    backend and the optional projector / fallback forward."""
 
+    def __init__(self, module, layer_index, backend, projector=None, fallback_forward=None):
+        self.module = module
+        self.layer_index = int(layer_index)
+        self.backend = backend
+        self.projector = projector
+        self.fallback_forward = fallback_forward
+        bind = getattr(projector, "bind", None)
+        if bind is not None:
+            bind(module)
 
-def _project_or_none(projector, module, x, rope_freqs, *, layer_index, transformer_options):
-    callback = getattr(projector, "try_project", None)
-    if callback is None:
-        callback = projector.project
-    return callback(module, x, rope_freqs, layer_index=layer_index, transformer_options=transformer_options)
+    @property
+    def backend_name(self):
+        return getattr(self.backend, "name", type(self.backend).__name__)
 
+    # -- the two routes ---------------------------------------------------------
 
-def _hnd_to_rows(out_hnd, module, backend):
-    if out_hnd.ndim != 4:
-        raise RuntimeError("%s returned rank-%d output; expected HND rank 4" % (_backend_name(backend), out_hnd.ndim))
-    out = out_hnd.transpose(1, 2).reshape(out_hnd.shape[0], out_hnd.shape[2], module.heads * module.head_dim)
-    return module.out_proj(out.squeeze(0))
+    def __call__(self, x, rope_freqs=None, transformer_options=None):
+        options = {} if transformer_options is None else transformer_options
+        if self.projector is not None:
+            carriers = self._ask_projector(x, rope_freqs, options)
+            if carriers is not None:
+                return self.projected(carriers, options)
+            if self.fallback_forward is not None:
+                return self.fallback_forward(x, rope_freqs=rope_freqs, transformer_options=options)
+        return self.unprojected(x, rope_freqs, options)
 
+    def _ask_projector(self, x, rope_freqs, options):
+        ask = getattr(self.projector, "try_project", None) or self.projector.project
+        return ask(self.module, x, rope_freqs, layer_index=self.layer_index, transformer_options=options)
 
-def _finish_projected(module, backend, prepared):
-    execute_projected = getattr(backend, "execute_projected", None)
-    if execute_projected is not None:
-        direct = execute_projected(module, prepared)
-        if direct is not None:
-            if direct.ndim != 2:
-                raise RuntimeError("%s returned rank-%d direct projected output; expected rank 2"
-                                   % (_backend_name(backend), direct.ndim))
-            return direct
-    return _hnd_to_rows(backend.execute(prepared), module, backend)
+    def projected(self, carriers, options):
+        prepared = self.backend.prepare_projected(carriers, layer_index=self.layer_index, transformer_options=options)
+        del carriers  # the carriers now belong to `prepared`
+        rows = self._rows_from_backend(prepared)
+        if rows is not None:
+            return rows
+        return self._out_proj(self.backend.execute(prepared))
+
+    def _rows_from_backend(self, prepared):
+        """A backend may finish the block itself and return ``(S, hidden)``."""
+        finish = getattr(self.backend, "execute_projected", None)
+        rows = None if finish is None else finish(self.module, prepared)
+        if rows is not None and rows.ndim != 2:
+            raise RuntimeError("%s returned rank-%d direct projected output; expected rank 2"
+                               % (self.backend_name, rows.ndim))
+        return rows
+
+    def unprojected(self, x, rope_freqs, options):
+        prepared = self.backend.prepare(*to_hnd(*project_qkv(self.module, x, rope_freqs)),
+                                        layer_index=self.layer_index, transformer_options=options)
+        return self._out_proj(self.backend.execute(prepared))
+
+    def _out_proj(self, out_hnd):
+        if out_hnd.ndim != 4:
+            raise RuntimeError("%s returned rank-%d output; expected HND rank 4" % (self.backend_name, out_hnd.ndim))
+        batch, _, sequence, _ = out_hnd.shape
+        rows = out_hnd.transpose(1, 2).reshape(batch, sequence, self.module.heads * self.module.head_dim)
+        return self.module.out_proj(rows.squeeze(0))
 
 
 def make_forward(module, layer_index, backend=None, projector=None, fallback_forward=None):
     """Build the replacement for ``module.forward`` of DiT block ``layer_index``."""
     if backend is None:
         raise ValueError("a backend is required: this package has no dense attention arm")
-    bind_projector = getattr(projector, "bind", None)
-    if bind_projector is not None:
-        bind_projector(module)
+    transaction = AttentionTransaction(module, layer_index, backend, projector, fallback_forward)
 
     def forward(x, rope_freqs=None, transformer_options=None):
-        transformer_options = transformer_options if transformer_options is not None else {}
-        if projector is not None:
-            projected = _project_or_none(projector, module, x, rope_freqs, layer_index=layer_index,
-                                         transformer_options=transformer_options)
-            if projected is not None:
-                prepared = backend.prepare_projected(projected, layer_index=layer_index,
-                                                     transformer_options=transformer_options)
-                del projected
-                try:
-                    return _finish_projected(module, backend, prepared)
-                finally:
-                    del prepared
-            if fallback_forward is not None:
-                return fallback_forward(x, rope_freqs=rope_freqs, transformer_options=transformer_options)
-
-        q, k, v = to_hnd(*project_qkv(module, x, rope_freqs))
-        prepared = backend.prepare(q, k, v, layer_index=layer_index, transformer_options=transformer_options)
-        del q, k, v
-        try:
-            out_hnd = backend.execute(prepared)
-        finally:
-            del prepared
-        return _hnd_to_rows(out_hnd, module, backend)
+        return transaction(x, rope_freqs, transformer_options)
 
     forward._h3_optimizations_attention = True
     forward._h3_optimizations_layer_index = int(layer_index)

@@ -250,19 +250,25 @@ class B200SparseBackend:
             retained = self.router._retained(video_budget, geometry)
             need_route = retained < geometry.pure_video_kv_tiles
             summary_dtype = torch.float64 if need_route else None
-            k_mean, v_scale = ops.column_stats(k if self.smooth_k else None, v, V_QUANT_BOUND)
-            # The V carrier depends on nothing but the statistics, and the router
-            # (latency bound, a tenth of the SMs' issue slots) leaves the GPU mostly
-            # idle: V is quantised on a second stream underneath the Q/K quantisers
-            # and the router, and joins before the carriers are handed out.
+            # Three chains share the GPU: the column statistics (K mean, V scale) and the V
+            # carrier that needs them run on a second stream; the Q quantiser, which needs
+            # neither, starts at once on the current one; the K quantiser joins when the
+            # statistics are in.  Each of these kernels alone leaves half of the memory
+            # system idle, and the router behind them is latency bound.  Every buffer is
+            # allocated on the current stream, which both chains rejoin before returning.
             main = torch.cuda.current_stream(q.device)
             side = self._side_stream(q.device)
+            k_mean, v_scale, scratch = ops.column_stats_buffers(heads, q.device, want_k_mean=self.smooth_k)
             v_carrier = ops.allocate_v_carrier(sequence, heads, v.device)
+            stats_done = torch.cuda.Event()
             side.wait_stream(main)
             try:
                 with torch.cuda.stream(side):
+                    ops.column_stats_into(k if self.smooth_k else None, v, k_mean, v_scale, scratch, V_QUANT_BOUND)
+                    stats_done.record(side)
                     ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
                 q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
+                main.wait_event(stats_done)
                 k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
                 if need_route:
                     route = self.router.build_route_from_summaries(
@@ -274,8 +280,8 @@ class B200SparseBackend:
                         q, k, snapshot.layout, video_budget, **self._sink(transformer_options, layer_index)
                     )
             finally:
-                # on every exit path the main stream is ordered after the V quantiser, so the
-                # allocator cannot hand v / v_scale / v_carrier to someone else while it still runs
+                # on every exit path the main stream is ordered after the second one, so the
+                # allocator cannot hand these buffers to someone else while it still runs
                 main.wait_stream(side)
         except SparseRouterError as exc:
             raise SparseSageError("sparse routing failed: %s" % exc) from exc
@@ -358,6 +364,22 @@ class B200SparseBackend:
                 "Sparse attention kernel failed: layer=%d sequence=%d heads=%d dtype=%s: %s"
                 % (sparse.layer_index, sparse.sequence, sparse.heads, sparse.output_dtype, exc)
             ) from exc
+
+    def forward(self, q, k, v, *, layer_index, transformer_options):
+        """``prepare`` + ``execute`` for a batch: every sparse backend of the
+        reference is limited to batch 1 (attention/sparse/sparse_sage.py:448-449)
+        and so are ``prepare`` / ``execute`` here; batch elements are independent,
+        so this entry walks them one after the other (one route per element) and
+        returns ``(B, H, S, 128)``."""
+        if q.ndim != 4 or q.shape != k.shape or q.shape != v.shape:
+            raise SparseSageError("forward expects equal rank-4 HND Q/K/V; got %s %s %s"
+                                  % (tuple(q.shape), tuple(k.shape), tuple(v.shape)))
+        outputs = []
+        for b in range(q.shape[0]):
+            prepared = self.prepare(q[b:b + 1], k[b:b + 1], v[b:b + 1], layer_index=layer_index,
+                                    transformer_options=transformer_options)
+            outputs.append(self.execute(prepared))
+        return outputs[0] if len(outputs) == 1 else torch.cat(outputs, dim=0)
 
     # -- host-resident activations -------------------------------------------
 

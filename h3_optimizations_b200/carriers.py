@@ -36,55 +36,62 @@ class PreparedFusedQKV:
     v_scale: torch.Tensor | None = None
 
 
-def validate_prepared_fused_qkv(prepared):
-    sequence = int(prepared.sequence)
-    heads = int(prepared.heads)
-    head_dim = int(prepared.head_dim)
-    shape = (1, heads, sequence, head_dim)
-    q_blocks = (sequence + Q_TILE - 1) // Q_TILE
-    k_blocks = (sequence + KV_TILE - 1) // KV_TILE
-    if head_dim != HEAD_DIM:
-        raise FusedQKVError("fused H3 QKV requires head_dim 128")
-    if tuple(prepared.q_int8.shape) != shape or tuple(prepared.k_int8.shape) != shape:
-        raise FusedQKVError("fused H3 Q/K carrier shape is invalid")
-    if prepared.q_int8.dtype != torch.int8 or prepared.k_int8.dtype != torch.int8:
-        raise FusedQKVError("fused H3 Q/K carriers must be INT8")
+def _carrier_spec(prepared):
+    """What each tensor of a ``PreparedFusedQKV`` must look like, as rows of
+    ``(field, tensor, shape, dtype | None, message)``, in the order they are checked."""
+    sequence, heads, head_dim = int(prepared.sequence), int(prepared.heads), int(prepared.head_dim)
+    q_blocks, k_blocks = -(-sequence // Q_TILE), -(-sequence // KV_TILE)
+    full = (1, heads, sequence, head_dim)
+    rows = [
+        ("q_int8", prepared.q_int8, full, None, "fused H3 Q/K carrier shape is invalid"),
+        ("k_int8", prepared.k_int8, full, None, "fused H3 Q/K carrier shape is invalid"),
+        ("q_int8", prepared.q_int8, None, torch.int8, "fused H3 Q/K carriers must be INT8"),
+        ("k_int8", prepared.k_int8, None, torch.int8, "fused H3 Q/K carriers must be INT8"),
+    ]
     if prepared.v_carrier is None:
         if prepared.v is None:
             raise FusedQKVError("fused H3 V is missing")
-        if tuple(prepared.v.shape) != shape or prepared.v.dtype != prepared.output_dtype:
-            raise FusedQKVError("fused H3 V carrier is invalid")
+        rows.append(("v", prepared.v, full, prepared.output_dtype, "fused H3 V carrier is invalid"))
     else:
-        padded = (sequence + 127) // 128 * 128
-        if tuple(prepared.v_carrier.shape) != (1, heads, head_dim, padded):
-            raise FusedQKVError("prepacked H3 FP8 V carrier shape is invalid")
-        if prepared.v_carrier.dtype != torch.float8_e4m3fn:
-            raise FusedQKVError("prepacked H3 V carrier must be E4M3 FP8")
+        padded = -(-sequence // 128) * 128
+        rows.append(("v_carrier", prepared.v_carrier, (1, heads, head_dim, padded), None,
+                     "prepacked H3 FP8 V carrier shape is invalid"))
+        rows.append(("v_carrier", prepared.v_carrier, None, torch.float8_e4m3fn, "prepacked H3 V carrier must be E4M3 FP8"))
         if prepared.v_scale is None:
             raise FusedQKVError("prepacked H3 FP8 V requires V scale")
-        if tuple(prepared.v_scale.shape) != (1, heads, head_dim):
-            raise FusedQKVError("prepacked H3 V scale shape is invalid")
-        if prepared.v_scale.dtype != torch.float32:
-            raise FusedQKVError("prepacked H3 V scale must be FP32")
-    if tuple(prepared.q_scale.shape) != (1, heads, q_blocks):
-        raise FusedQKVError("fused H3 Q scale shape is invalid")
-    if tuple(prepared.k_scale.shape) != (1, heads, k_blocks):
-        raise FusedQKVError("fused H3 K scale shape is invalid")
-    if prepared.q_scale.dtype != torch.float32 or prepared.k_scale.dtype != torch.float32:
-        raise FusedQKVError("fused H3 Q/K scales must be float32")
-    if tuple(prepared.q_summary.shape) != (1, heads, q_blocks, head_dim):
-        raise FusedQKVError("fused H3 Q router summary shape is invalid")
-    if tuple(prepared.k_summary.shape) != (1, heads, k_blocks, head_dim):
-        raise FusedQKVError("fused H3 K router summary shape is invalid")
-    tensors = [prepared.q_int8, prepared.q_scale, prepared.k_int8, prepared.k_scale,
-               prepared.q_summary, prepared.k_summary]
-    for extra in (prepared.v, prepared.v_carrier, prepared.v_scale):
-        if extra is not None:
-            tensors.append(extra)
-    if any(t.device != prepared.q_int8.device for t in tensors):
+        rows.append(("v_scale", prepared.v_scale, (1, heads, head_dim), None, "prepacked H3 V scale shape is invalid"))
+        rows.append(("v_scale", prepared.v_scale, None, torch.float32, "prepacked H3 V scale must be FP32"))
+    rows += [
+        ("q_scale", prepared.q_scale, (1, heads, q_blocks), None, "fused H3 Q scale shape is invalid"),
+        ("k_scale", prepared.k_scale, (1, heads, k_blocks), None, "fused H3 K scale shape is invalid"),
+        ("q_scale", prepared.q_scale, None, torch.float32, "fused H3 Q/K scales must be float32"),
+        ("k_scale", prepared.k_scale, None, torch.float32, "fused H3 Q/K scales must be float32"),
+        ("q_summary", prepared.q_summary, (1, heads, q_blocks, head_dim), None, "fused H3 Q router summary shape is invalid"),
+        ("k_summary", prepared.k_summary, (1, heads, k_blocks, head_dim), None, "fused H3 K router summary shape is invalid"),
+    ]
+    return rows
+
+
+def validate_prepared_fused_qkv(prepared):
+    """Check a projector's output against the carrier contract
+    (attention/sparse/fused_qkv.py:95-154: same conditions, same
+    ``FusedQKVError`` texts) and hand it back.  The conditions are a table
+    (``_carrier_spec``) walked once; device and contiguity are checked over
+    every tensor the table names."""
+    if int(prepared.head_dim) != HEAD_DIM:
+        raise FusedQKVError("fused H3 QKV requires head_dim 128")
+    seen = {}
+    for name, tensor, shape, dtype, message in _carrier_spec(prepared):
+        if shape is not None and tuple(tensor.shape) != shape:
+            raise FusedQKVError(message)
+        if dtype is not None and tensor.dtype != dtype:
+            raise FusedQKVError(message)
+        seen[name] = tensor
+    home = prepared.q_int8.device
+    if any(tensor.device != home for tensor in seen.values()):
         raise FusedQKVError("fused H3 QKV carrier devices differ")
-    contiguous = [t for t in tensors if t is not prepared.v]
-    if any(not t.is_contiguous() for t in contiguous):
+    # V in floating point may be a strided view of the projection; everything else is dense
+    if any(not tensor.is_contiguous() for name, tensor in seen.items() if name != "v"):
         raise FusedQKVError("fused H3 QKV carriers must be contiguous")
     return prepared
 

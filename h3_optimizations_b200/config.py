@@ -1,9 +1,9 @@
 """Density parameters of the H3 Sparse Attention (and Advanced) nodes.
 
-Mirrors ``HybridSparseConfig`` / ``resolve_video_budget`` of the reference
-(attention/sparse/config.py:25-129): a fixed video-KV budget with optional
-explicit early/late step windows, the legacy "+0.30 on the first and last two
-steps" switch, or a static per-layer table.
+The field names, defaults, constants and error texts are the contract of the
+reference's node parameters (attention/sparse/config.py:25-129); how a budget
+is validated and resolved is organised here as a short list of rules, each a
+function that either decides the budget of a (sampler step, layer) or passes.
 """
 
 from __future__ import annotations
@@ -19,13 +19,23 @@ DENSITY_FIXED = "fixed"
 DENSER_EARLY_LATE_STEP_COUNT = 2
 DENSER_EARLY_LATE_BONUS = 0.30
 
+_WINDOW_FIELDS = ("early_steps", "early_kv", "late_steps", "late_kv")
 
-def _validate_budget(name, value):
+
+def _density(name, value):
+    """A KV density as float; ``None`` passes through."""
     if value is None:
-        return
-    budget = float(value)
-    if not math.isfinite(budget) or not 0.01 <= budget <= 1.0:
+        return None
+    number = float(value)
+    if not (math.isfinite(number) and 0.01 <= number <= 1.0):
         raise ValueError("%s must be finite and in [0.01, 1]" % name)
+    return number
+
+
+def _step_count(name, value):
+    if isinstance(value, bool) or int(value) != value or int(value) < 0:
+        raise ValueError("%s must be a non-negative integer" % name)
+    return int(value)
 
 
 @dataclass(frozen=True)
@@ -43,82 +53,106 @@ class HybridSparseConfig:
 
     def __post_init__(self):
         if self.mode not in IMPLEMENTED_MODES:
-            raise ValueError(
-                "sparse mode %r is unavailable; implemented modes: %s"
-                % (self.mode, ", ".join(IMPLEMENTED_MODES))
-            )
-        _validate_budget("video_budget", self.video_budget)
-        _validate_budget("early_kv", self.early_kv)
-        _validate_budget("late_kv", self.late_kv)
-        if self.layer_video_budgets is not None:
-            budgets = tuple(float(v) for v in self.layer_video_budgets)
-            if len(budgets) != H3_LAYER_COUNT:
-                raise ValueError("layer_video_budgets must contain exactly %d values" % H3_LAYER_COUNT)
-            for index, budget in enumerate(budgets):
-                _validate_budget("layer_video_budgets[%d]" % index, budget)
-            object.__setattr__(self, "layer_video_budgets", budgets)
+            raise ValueError("sparse mode %r is unavailable; implemented modes: %s"
+                             % (self.mode, ", ".join(IMPLEMENTED_MODES)))
         if self.density_mode != DENSITY_FIXED:
             raise ValueError("only fixed Sparse Sage density is supported")
-        explicit = (self.early_steps, self.early_kv, self.late_steps, self.late_kv)
-        if any(v is not None for v in explicit):
-            if not all(v is not None for v in explicit):
+        for name in ("video_budget", "early_kv", "late_kv"):
+            _density(name, getattr(self, name))
+
+        table = self.layer_video_budgets
+        if table is not None:
+            table = tuple(float(entry) for entry in table)
+            if len(table) != H3_LAYER_COUNT:
+                raise ValueError("layer_video_budgets must contain exactly %d values" % H3_LAYER_COUNT)
+            for layer, entry in enumerate(table):
+                _density("layer_video_budgets[%d]" % layer, entry)
+            object.__setattr__(self, "layer_video_budgets", table)
+
+        given = [name for name in _WINDOW_FIELDS if getattr(self, name) is not None]
+        if given:
+            if len(given) != len(_WINDOW_FIELDS):
                 raise ValueError("explicit early/late sparse schedule is incomplete")
             if self.denser_early_late_steps:
                 raise ValueError("legacy and explicit early/late schedules cannot be combined")
-            for name, value in (("early_steps", self.early_steps), ("late_steps", self.late_steps)):
-                if isinstance(value, bool) or int(value) != value or int(value) < 0:
-                    raise ValueError("%s must be a non-negative integer" % name)
-        if self.layer_video_budgets is not None and (
-            self.denser_early_late_steps or self.early_steps is not None
-        ):
+            _step_count("early_steps", self.early_steps)
+            _step_count("late_steps", self.late_steps)
+        if table is not None and (given or self.denser_early_late_steps):
             raise ValueError("static per-layer budgets cannot be combined with early/late schedules")
 
     @property
+    def has_windows(self):
+        return self.early_steps is not None
+
+    @property
     def signature(self):
+        def cast(kind, value):
+            return None if value is None else kind(value)
+
         return (
-            self.mode,
-            float(self.video_budget),
-            bool(self.strict),
-            self.density_mode,
+            self.mode, float(self.video_budget), bool(self.strict), self.density_mode,
             bool(self.denser_early_late_steps),
-            None if self.early_steps is None else int(self.early_steps),
-            None if self.early_kv is None else float(self.early_kv),
-            None if self.late_steps is None else int(self.late_steps),
-            None if self.late_kv is None else float(self.late_kv),
+            cast(int, self.early_steps), cast(float, self.early_kv),
+            cast(int, self.late_steps), cast(float, self.late_kv),
             self.layer_video_budgets,
         )
 
 
-def resolve_video_budget(config, step_index, total_steps, layer_index=None):
-    """Budget for one (sampler step, layer); same precedence as the reference:
-    per-layer table, explicit windows (overlap -> the denser), legacy bonus,
-    base budget.  A step outside ``[0,total)`` resolves to the base budget."""
-    if config.layer_video_budgets is not None:
-        if layer_index is None:
-            raise ValueError("layer_index is required for static per-layer budgets")
-        if isinstance(layer_index, bool) or int(layer_index) != layer_index:
-            raise ValueError("layer_index must be an integer")
-        layer_index = int(layer_index)
-        if not 0 <= layer_index < len(config.layer_video_budgets):
-            raise ValueError("layer_index is outside the static per-layer budget table")
-        return float(config.layer_video_budgets[layer_index])
-    budget = float(config.video_budget)
-    step_index = int(step_index)
-    total_steps = int(total_steps)
-    if step_index < 0 or total_steps <= 0 or step_index >= total_steps:
-        return budget
-    if config.early_steps is not None:
-        in_early = step_index < int(config.early_steps)
-        in_late = step_index >= total_steps - int(config.late_steps)
-        if in_early and in_late:
-            return max(float(config.early_kv), float(config.late_kv))
-        if in_early:
-            return float(config.early_kv)
-        if in_late:
-            return float(config.late_kv)
-        return budget
+# -- budget rules, tried in this order; the first that answers wins -------------
+
+
+def _from_layer_table(config, step, total, layer):
+    table = config.layer_video_budgets
+    if table is None:
+        return None
+    if layer is None:
+        raise ValueError("layer_index is required for static per-layer budgets")
+    if isinstance(layer, bool) or int(layer) != layer:
+        raise ValueError("layer_index must be an integer")
+    if not 0 <= int(layer) < len(table):
+        raise ValueError("layer_index is outside the static per-layer budget table")
+    return table[int(layer)]
+
+
+def _outside_the_run(config, step, total, layer):
+    """An unknown step (-1), an empty run or a step past its end: base budget."""
+    if step < 0 or total <= 0 or step >= total:
+        return float(config.video_budget)
+    return None
+
+
+def _from_windows(config, step, total, layer):
+    if not config.has_windows:
+        return None
+    hits = []
+    if step < int(config.early_steps):
+        hits.append(float(config.early_kv))
+    if step >= total - int(config.late_steps):
+        hits.append(float(config.late_kv))
+    # inside both windows the denser one applies; outside both the base budget
+    return max(hits) if hits else float(config.video_budget)
+
+
+def _from_legacy_bonus(config, step, total, layer):
     if not config.denser_early_late_steps:
-        return budget
-    if step_index < DENSER_EARLY_LATE_STEP_COUNT or step_index >= total_steps - DENSER_EARLY_LATE_STEP_COUNT:
-        return min(1.0, budget + DENSER_EARLY_LATE_BONUS)
-    return budget
+        return None
+    edge = DENSER_EARLY_LATE_STEP_COUNT
+    if step < edge or step >= total - edge:
+        return min(1.0, float(config.video_budget) + DENSER_EARLY_LATE_BONUS)
+    return None
+
+
+_RULES = (_from_layer_table, _outside_the_run, _from_windows, _from_legacy_bonus)
+
+
+def resolve_video_budget(config, step_index, total_steps, layer_index=None):
+    """Video-KV budget of one (sampler step, layer): static per-layer table,
+    else the base budget outside ``[0, total_steps)``, else explicit early/late
+    windows, else the legacy bonus on the first and last two steps, else the
+    base budget (attention/sparse/config.py:94-129)."""
+    step, total = int(step_index), int(total_steps)
+    for rule in _RULES:
+        budget = rule(config, step, total, layer_index)
+        if budget is not None:
+            return float(budget)
+    return float(config.video_budget)

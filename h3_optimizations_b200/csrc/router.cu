@@ -3,7 +3,10 @@
 //
 // One CTA scores 8 pure-video query tiles of one head against every
 // pure-video KV tile with FP64 tensor-core MMAs (scores kept in shared
-// memory), then each warp owns one row: an 8-pass MSB-first radix select on
+// memory).  The K tile means are brought in 64 tiles at a time by the whole
+// CTA with coalesced loads (every thread has 32 independent loads in flight)
+// and widened to FP64 in shared memory; the MMA operands are then read from
+// there.  Each warp then owns one row: an 8-pass MSB-first radix select on
 // order-preserving 64-bit keys finds the retained-th largest score exactly,
 // and a ballot-ordered sweep writes the surviving tile indices in ascending
 // order, so no sort is needed.
@@ -13,6 +16,10 @@ namespace h3s {
 
 constexpr int kRouteRows = 8;         // query tiles per CTA == warps per CTA
 constexpr int kRouteThreads = kRouteRows * 32;
+constexpr int kRouteKBlock = 64;       // KV tiles staged per round: one 8-tile MMA block per warp
+// Row stride of the staged block in doubles: 128 channels + 4 of padding, so the
+// 16 lanes of a half warp (4 tiles x 4 channels) read 16 different 8-byte banks.
+constexpr int kRouteKStride = H3S_HEAD_DIM + 4;
 
 template <typename T> __device__ __forceinline__ double to_double(T v);
 template <> __device__ __forceinline__ double to_double<double>(double v) { return v; }
@@ -35,7 +42,8 @@ route_topk_kernel(const T *__restrict__ q_summary, const T *__restrict__ k_summa
   const int pure_q = q_stop - q_start;
   const int pure_kv = kv_stop - kv_start;
   double *scores = reinterpret_cast<double *>(smem_raw);                                     // [kRouteRows][pure_kv]
-  int *hist = reinterpret_cast<int *>(scores + static_cast<size_t>(kRouteRows) * pure_kv);  // [rows][256]
+  double *k_block = scores + static_cast<size_t>(kRouteRows) * pure_kv;                     // [kRouteKBlock][kRouteKStride]
+  int *hist = reinterpret_cast<int *>(k_block + kRouteKBlock * kRouteKStride);              // [rows][256]
 
   const int head = blockIdx.y;
   const int row0 = blockIdx.x * kRouteRows;
@@ -45,8 +53,7 @@ route_topk_kernel(const T *__restrict__ q_summary, const T *__restrict__ k_summa
   // ---- scores[r][p] = <q[r], k[p]> in FP64 on the tensor cores ----
   // mma.m8n8k4.f64: A is the CTA's 8 query tiles x 4 channels, B 4 channels x 8
   // KV tiles; lane l holds A[l/4][l%4], B[l%4][l/4] and C[l/4][2*(l%4) + {0,1}].
-  // The 32 A fragments of a lane (all 128 channels) stay in registers; every
-  // warp walks its own KV blocks and reads the K means straight from L2.
+  // The 32 A fragments of a lane (all 128 channels) stay in registers.
   {
     const int frag_row = lane >> 2, frag_k = lane & 3;
     const int a_row = min(row0 + frag_row, pure_q - 1);
@@ -54,19 +61,34 @@ route_topk_kernel(const T *__restrict__ q_summary, const T *__restrict__ k_summa
     double a[H3S_HEAD_DIM / 4];
 #pragma unroll
     for (int kk = 0; kk < H3S_HEAD_DIM / 4; ++kk) a[kk] = to_double(qp[4 * kk]);
-    const int n_blocks = (pure_kv + 7) >> 3;
-    for (int nb = warp; nb < n_blocks; nb += kRouteRows) {
-      const int b_row = min(8 * nb + frag_row, pure_kv - 1);
-      const T *kp = k_summary + (static_cast<int64_t>(head) * kv_tiles + kv_start + b_row) * H3S_HEAD_DIM + frag_k;
+    const T *k_head = k_summary + (static_cast<int64_t>(head) * kv_tiles + kv_start) * H3S_HEAD_DIM;
+    for (int base = 0; base < pure_kv; base += kRouteKBlock) {
+      // stage tiles [base, base + 64): element e of the block is channel e % 128 of tile e / 128
+      constexpr int kPerThread = kRouteKBlock * H3S_HEAD_DIM / kRouteThreads;  // 32
+      T staged[kPerThread];
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        const int e = i * kRouteThreads + threadIdx.x;
+        const int tile = min(base + (e >> 7), pure_kv - 1);  // rows past the end repeat the last tile
+        staged[i] = k_head[static_cast<int64_t>(tile) * H3S_HEAD_DIM + (e & 127)];
+      }
+      __syncthreads();  // the previous round's readers are done with k_block
+#pragma unroll
+      for (int i = 0; i < kPerThread; ++i) {
+        const int e = i * kRouteThreads + threadIdx.x;
+        k_block[(e >> 7) * kRouteKStride + (e & 127)] = to_double(staged[i]);
+      }
+      __syncthreads();
+      const double *kp = k_block + (8 * warp + frag_row) * kRouteKStride + frag_k;
       double c0 = 0.0, c1 = 0.0;
 #pragma unroll
       for (int kk = 0; kk < H3S_HEAD_DIM / 4; ++kk) {
-        const double b = to_double(kp[4 * kk]);
+        const double b = kp[4 * kk];
         asm volatile("mma.sync.aligned.m8n8k4.row.col.f64.f64.f64.f64 {%0,%1}, {%2}, {%3}, {%0,%1};"
                      : "+d"(c0), "+d"(c1)
                      : "d"(a[kk]), "d"(b));
       }
-      const int col = 8 * nb + 2 * frag_k;
+      const int col = base + 8 * warp + 2 * frag_k;
       if (col < pure_kv) scores[static_cast<size_t>(frag_row) * pure_kv + col] = c0;
       if (col + 1 < pure_kv) scores[static_cast<size_t>(frag_row) * pure_kv + col + 1] = c1;
     }
@@ -165,7 +187,8 @@ static int launch_route(const void *q_summary, const void *k_summary, int heads,
                         int q_start, int q_stop, int kv_start, int kv_stop, int retained, int route_len,
                         int32_t *route, cudaStream_t stream) {
   const int pure_q = q_stop - q_start, pure_kv = kv_stop - kv_start;
-  const size_t smem = sizeof(double) * static_cast<size_t>(kRouteRows) * pure_kv + sizeof(int) * kRouteRows * 256;
+  const size_t smem = sizeof(double) * (static_cast<size_t>(kRouteRows) * pure_kv + kRouteKBlock * kRouteKStride) +
+                      sizeof(int) * kRouteRows * 256;
   H3S_CHECK_ARG(smem <= 220 * 1024, "route_topk: %d pure-video KV tiles need %zu bytes of shared memory", pure_kv, smem);
   H3S_CHECK_CUDA(cudaFuncSetAttribute(route_topk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   dim3 grid(ceil_div(pure_q, kRouteRows), heads);

@@ -51,16 +51,34 @@ def set_wait_budget_ns(nanoseconds):
     return previous
 
 
+def column_stats_buffers(heads, device, want_k_mean=True, want_v_scale=True):
+    """``(k_mean | None, v_scale | None, scratch)`` for ``column_stats_into``."""
+    lib = _native.load()
+    scratch = torch.empty(lib.h3s_column_stats_scratch_bytes(int(heads)), dtype=torch.uint8, device=device)
+    k_mean = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=device) if want_k_mean else None
+    v_scale = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=device) if want_v_scale else None
+    return k_mean, v_scale, scratch
+
+
 def column_stats(k=None, v=None, v_bound=FP8_V_BOUND):
     """``(k_mean (1,H,128) | None, v_scale (1,H,128) | None)``."""
+    ref = k if k is not None else v
+    heads, _ = _hnd(ref, "column_stats input")
+    k_mean, v_scale, scratch = column_stats_buffers(heads, ref.device, k is not None, v is not None)
+    return column_stats_into(k, v, k_mean, v_scale, scratch, v_bound)
+
+
+def column_stats_into(k, v, k_mean, v_scale, scratch, v_bound=FP8_V_BOUND):
+    """``column_stats`` into caller-owned outputs and scratch (all from
+    ``column_stats_buffers``), so that the launch can go to a stream other than
+    the one the buffers were allocated on."""
     lib = _native.load()
     ref = k if k is not None else v
     heads, sequence = _hnd(ref, "column_stats input")
     if k is not None and v is not None and (k.shape != v.shape or k.dtype != v.dtype):
         raise _native.NativeError("column_stats: K and V must share shape and dtype")
-    scratch = torch.empty(lib.h3s_column_stats_scratch_bytes(heads), dtype=torch.uint8, device=ref.device)
-    k_mean = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=ref.device) if k is not None else None
-    v_scale = torch.empty((1, heads, HEAD_DIM), dtype=torch.float32, device=ref.device) if v is not None else None
+    if (k is not None and k_mean is None) or (v is not None and v_scale is None):
+        raise _native.NativeError("column_stats: an output buffer is missing")
     check(
         lib.h3s_column_stats(
             ptr(k), k.stride(1) if k is not None else 0, k.stride(2) if k is not None else 0,

@@ -76,7 +76,7 @@ CONFIG4 = SequenceSpec(
     _segments(("text", 512), ("ref_img", 1024), ("audio", 1536), ("video", 32760)),
     (21, 30, 52), audio_t=768,
 )
-# The order BASELINE's prose uses (video first); the reference router rejects
+# Video first, text after it (the order the benchmark description words it in); the reference router rejects
 # it, the generalised router here accepts it.
 CONFIG0_VIDEO_FIRST = SequenceSpec(
     "config0_video_first", 4, _segments(("video", 2048), ("text", 256)), (1, 32, 64)

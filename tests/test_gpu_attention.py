@@ -134,7 +134,7 @@ def test_video_first_layout(ops):
 
 
 def test_config0_through_the_backend(ops):
-    """BASELINE config 0 end to end through the plug-in surface: prepare()
+    """The small CPU-sized case (4 heads, 256 text + 2048 video tokens) end to end through the plug-in surface: prepare()
     (stats, quantisation, routing) + execute(), FP32 inputs."""
     from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, runtime_options
 
@@ -163,7 +163,7 @@ def test_config0_through_the_backend(ops):
 
 
 def test_config1_full_size_sampled_against_oracle_and_cross_checked(ops):
-    """BASELINE config 1 (24 heads x 33272 tokens, 30 %): the whole layer runs
+    """The benchmark layer (24 heads x 33272 tokens, 30 %): the whole layer runs
     on the GPU; the CPU oracle checks a sample of (head, query tile) pairs -
     dense, first/last routed and the ragged tail - and the mma.sync kernel
     cross-checks every output row."""

@@ -103,7 +103,7 @@ def test_known_answers_full_budget_and_ties(router):
 
 
 def test_generalised_layout_video_first(router):
-    """BASELINE's prose orders video before text; the reference router rejects
+    """The benchmark description words the layout as video followed by text; the reference router rejects
     that layout, this router treats every tile outside the video range as dense."""
     from h3_optimizations_b200.errors import SparseRouterError
     from h3_optimizations_b200.router import SparseTileRouter

@@ -64,7 +64,7 @@ def test_density_schedule_matches_reference_tables(golden_dir):
         layer = 7 if config.layer_video_budgets is not None else None
         for step, expected in table["budgets"]:
             assert resolve_video_budget(config, step, table["total_steps"], layer) == expected
-    # BASELINE config 3: 30 steps, 2 early and 2 late at 50 %, the rest at 30 %
+    # the long-sequence schedule: 30 steps, 2 early and 2 late at 50 %, the rest at 30 %
     config = HybridSparseConfig(video_budget=0.3, early_steps=2, early_kv=0.5, late_steps=2, late_kv=0.5)
     budgets = [resolve_video_budget(config, s, 30) for s in range(30)]
     assert budgets == [0.5, 0.5] + [0.3] * 26 + [0.5, 0.5]

@@ -52,8 +52,14 @@ def test_two_calls_in_a_row_match_the_entry_point_with_caller_scratch(native_lib
         want_mean, want_scale = ops.column_stats(k, v)
         got_mean = torch.full((1, heads, 128), float("nan"), dtype=torch.float32, device="cuda")
         got_scale = torch.full_like(got_mean, float("nan"))
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         _call_static(native_lib, k, v, got_mean, got_scale)
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        # device memory in use is the same before and after: the call allocated nothing, not
+        # through torch's pool (the ABI knows nothing of it) and not from the driver either
+        assert free_after == free_before, "the call changed the device's free memory by %d bytes" % (free_before - free_after)
         # the V scale is a maximum: order independent, so identical
         assert torch.equal(got_scale, want_scale)
         # the K mean is an FP64 sum gathered with atomics whose order varies from
