@@ -60,9 +60,10 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=10)
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", choices=("native", "reference"), default="native")
-    parser.add_argument("--config", choices=("config1", "config2", "config3"), default="config1",
+    parser.add_argument("--config", choices=("config1", "config2", "config3", "config4"), default="config1",
                         help="config1 is the headline workload; config2 adds the chunked QKV projection in front; "
-                             "config3 is the 76112-token sequence")
+                             "config3 is the 76112-token sequence; config4 is the mixed-modality block with batch 2, "
+                             "out_proj and the chunked FP8 MLP behind the attention")
     parser.add_argument("--schedule", action="store_true",
                         help="run the 30-step sampler schedule (budgets 0.5, 0.5, 0.3 x 26, 0.5, 0.5) instead of one budget")
     parser.add_argument("--exchange", choices=("auto", "peer", "nccl"), default="auto",
@@ -719,10 +720,128 @@ def run_config2(args, spec, stdout):
         dist.destroy_process_group()
 
 
+def run_config4(args, spec, stdout):
+    """Mixed-modality DiT block, batch 2: text + reference + audio + video
+    tokens, only video x video tiles sparse; attention, then out_proj (bf16) and
+    the chunked FP8-E4M3 MLP 3072 -> 12288 (GELU-tanh) -> 3072 in 4096-token
+    chunks.  Batch elements and heads are both independent units on the attention
+    path, so the 2 x 24 (batch, head) pairs are sharded over the ranks like 48
+    heads; behind the exchange every rank runs out_proj and the MLP on its share
+    of the 2 x 35832 token rows."""
+    import torch.distributed as dist
+
+    from h3_optimizations_b200 import B200SparseBackend, HybridSparseConfig, ops, runtime_options
+    from h3_optimizations_b200.mlp import ChunkedFP8MLP
+    from h3_optimizations_b200.sharding import HeadShardedBackend, head_partition
+
+    world, rank, local_rank, device = init_ranks(args)
+    batch, hidden, ffn = 2, 3072, 12288
+    units = batch * spec.heads
+    u0, u1 = head_partition(units, world, rank)
+    pieces = []
+    for unit in range(u0, u1):  # unit = batch element * heads + head; every batch element has its own seed
+        b, head = divmod(unit, spec.heads)
+        pieces.append(workloads.structured_qkv(spec, seed=b, heads=[head]))
+    q, k, v = (torch.cat([p[i] for p in pieces], dim=1).to(device) for i in range(3))
+    gen = torch.Generator().manual_seed(7)
+    w_out = (torch.randn((hidden, spec.heads * HEAD_DIM), generator=gen) * 0.02).to(torch.bfloat16).to(device)
+    mlp = ChunkedFP8MLP(torch.randn((ffn, hidden), generator=gen) * 0.02, torch.zeros(ffn),
+                        torch.randn((hidden, ffn), generator=gen) * 0.02, torch.zeros(hidden)).to(device)
+    backend = B200SparseBackend(HybridSparseConfig(video_budget=args.budget))
+    sharded = HeadShardedBackend(backend, units, exchange=args.exchange) if world > 1 else None
+    owner = sharded if sharded is not None else backend
+    options = runtime_options(spec.layout(), step_index=5, total_steps=30)
+    total_rows = batch * spec.sequence
+    r0, r1 = head_partition(total_rows, world, rank)  # this rank's token rows of the (batch * S, hidden) activations
+    marks = []
+
+    def step(record=False):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(5)] if record else None
+        if record: e[0].record()
+        prepared = owner.prepare(q, k, v, layer_index=0, transformer_options=options)
+        if record: e[1].record()
+        out = owner.execute(prepared)                                        # (1, units, S, 128) on every rank
+        if record: e[2].record()
+        # (batch, heads, S, 128) -> token-major rows (batch * S, heads * 128) of this rank's share
+        by_token = out.view(batch, spec.heads, spec.sequence, HEAD_DIM).permute(0, 2, 1, 3)   # (batch, S, heads, 128)
+        parts = []
+        for b in range(batch):
+            s0, s1 = max(r0 - b * spec.sequence, 0), min(r1 - b * spec.sequence, spec.sequence)
+            if s0 < s1:
+                parts.append(by_token[b, s0:s1].reshape(s1 - s0, spec.heads * HEAD_DIM))
+        rows = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+        rows = rows if rows.is_contiguous() else rows.contiguous()
+        y = ops.dense_gemm(rows, w_out)
+        if record: e[3].record()
+        z = mlp(y)
+        if record:
+            e[4].record(); marks.append(e)
+        return z, prepared.sparse
+
+    def fence():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    sparse = None
+    for _ in range(args.warmup):
+        _, sparse = step()
+    fence()
+    sampler.mark_begin()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    wall0 = time.perf_counter()
+    t0.record()
+    for _ in range(args.steps):
+        _, sparse = step(record=True)
+    t1.record(); fence()
+    region_seconds = time.perf_counter() - wall0
+    clocks = sampler.stop() if rank == 0 else None
+    stage = [statistics.mean(m[i].elapsed_time(m[i + 1]) for m in marks) for i in range(4)]
+    worst = torch.tensor([t0.elapsed_time(t1) / args.steps] + stage, dtype=torch.float64, device=device)
+    local = torch.tensor([float(attention_ops(spec, sparse.route.indices, sparse.route.geometry, u1 - u0)),
+                          2.0 * (r1 - r0) * hidden * spec.heads * HEAD_DIM, 4.0 * (r1 - r0) * hidden * ffn],
+                         dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(local, op=dist.ReduceOp.SUM)
+    if rank == 0:
+        peaks, peak_source = measured_peaks()
+        step_ms, prep_ms, attn_ms, proj_ms, mlp_ms = (float(t) for t in worst)
+        attn_ops, proj_ops, mlp_ops = (float(t) for t in local)
+        mlp_tops = mlp_ops / world / (mlp_ms * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": (attn_ops + proj_ops + mlp_ops) / (step_ms * 1e-3) / 1e12, "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 QK^T / fp8-e4m3 PV; bf16 out_proj; fp8-e4m3 MLP", "data": "synthetic",
+            "config": {"workload": "config4: B2 H%d D128, %d tokens per batch element (%s), video x video tiles sparse at %.0f%%, "
+                                   "then out_proj %d->%d (bf16) and FP8-E4M3 MLP %d->%d (GELU-tanh)->%d in 4096-token chunks"
+                                   % (spec.heads, spec.sequence, " + ".join("%d %s" % (b - a, kind) for a, b, kind in spec.segments),
+                                      args.budget * 100, spec.heads * HEAD_DIM, hidden, hidden, ffn, hidden),
+                       "parallelism": "%d (batch, head) units and %d token rows sharded x%d" % (units, total_rows, world),
+                       "exchange": sharded.exchange_note if sharded is not None else "none",
+                       "algorithmic_ops": {"attention": attn_ops, "out_proj": proj_ops, "mlp": mlp_ops},
+                       "l2_policy": "Q,K,V (%.0f MB per GPU) exceed the 126 MB L2; no flush"
+                                    % ((u1 - u0) * spec.sequence * HEAD_DIM * 2 * 3 / 1e6)},
+            "stages_ms": {"prepare": prep_ms, "attention (+ exchange)": attn_ms, "out_proj": proj_ms, "fp8 mlp": mlp_ms},
+            "roofline": tensor_roofline("qkv_gemm_kernel<dense> (FP8 MLP: two GEMMs + two row quantisers)", mlp_tops, peaks,
+                                        peak_source, region_seconds, None),
+            "clocks": clocks,
+            "gpu_launches": args.steps * (7 + 1 + 4 * ((r1 - r0 + 4095) // 4096)),
+        }
+        stdout.emit(line)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     stdout = Stdout()
-    spec = {"config1": workloads.CONFIG1, "config2": workloads.CONFIG1, "config3": workloads.CONFIG3}[args.config]
+    spec = {"config1": workloads.CONFIG1, "config2": workloads.CONFIG1, "config3": workloads.CONFIG3,
+            "config4": workloads.CONFIG4}[args.config]
     if args.heads:
         import dataclasses
 
@@ -731,6 +850,8 @@ def main():
         run_reference(args, spec, stdout)
     elif args.config == "config2":
         run_config2(args, spec, stdout)
+    elif args.config == "config4":
+        run_config4(args, spec, stdout)
     else:
         run_attention(args, spec, stdout)
 

@@ -69,6 +69,9 @@ PROTOTYPES = {
     "h3s_qkv_gemm_chunk_carriers": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             ctypes.POINTER(QKVCarriers), c_void_p, c_void_p, c_float, c_void_p,
                                             c_int, c_void_p, c_void_p, c_void_p]),
+    "h3s_dense_gemm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                               c_void_p, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+    "h3s_quant_rows_fp8": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "h3s_column_stats_finalize": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "h3s_route_topk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_void_p]),

@@ -365,6 +365,33 @@ class B200SparseBackend:
                 % (sparse.layer_index, sparse.sequence, sparse.heads, sparse.output_dtype, exc)
             ) from exc
 
+    def execute_projected(self, module, prepared):
+        """Attention followed by the block's ``out_proj`` on the tensor cores:
+        returns ``(S, hidden)`` as the forward boundary allows a backend to do
+        (attention_forward.py:99-128; the reference's streamed backend does it in
+        attention/sparse/sparse_sage_streamed.py:1454-1472).  The attention output
+        is written token-major, so its ``(S, heads*128)`` view feeds the GEMM
+        without a copy.  Returns ``None`` - the caller then runs ``execute`` and
+        the module's own ``out_proj`` - when the projection is not a plain bf16
+        Linear on the attention's device."""
+        linear = getattr(module, "out_proj", None)
+        weight = getattr(linear, "weight", None)
+        sparse = prepared.sparse
+        if (weight is None or weight.ndim != 2 or weight.dtype != torch.bfloat16
+                or weight.dtype != sparse.output_dtype or weight.device != sparse.q_int8.device
+                or weight.shape[1] != sparse.heads * 128 or weight.shape[0] % 8 or weight.stride(1) != 1):
+            return None
+        out_hnd = self.execute(prepared)                                   # (1, H, S, 128) view of (S, H, 128)
+        rows = out_hnd.permute(0, 2, 1, 3).reshape(sparse.sequence, sparse.heads * 128)
+        if rows.data_ptr() != out_hnd.data_ptr():                          # never a copy with this backend's buffers
+            rows = rows.contiguous()
+        bias = getattr(linear, "bias", None)
+        try:
+            result = ops.dense_gemm(rows, weight, bias=None if bias is None else bias.detach().float().contiguous())
+        except _native.NativeError as exc:
+            raise SparseSageError("output projection failed: layer=%d: %s" % (sparse.layer_index, exc)) from exc
+        return result
+
     def forward(self, q, k, v, *, layer_index, transformer_options):
         """``prepare`` + ``execute`` for a batch: every sparse backend of the
         reference is limited to batch 1 (attention/sparse/sparse_sage.py:448-449)

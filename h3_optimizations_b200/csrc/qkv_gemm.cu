@@ -19,6 +19,8 @@
 //                        K (when smoothed) and V, which need whole-sequence
 //                        statistics, are staged as bf16 while their column sums
 //                        / maxima are accumulated for the short second phase.
+#include <cstring>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tma.cuh"
@@ -128,8 +130,16 @@ constexpr uint32_t kEpilogueTileBytes = kGemmM * H3S_HEAD_DIM * 2;  // one half 
 // that it can be re-read column-wise (quantisation, statistics and every global
 // store then run on contiguous lines); it pays for the two 32 KB staging tiles
 // with one stage of the operand ring.
-template <bool kCarriers>
+// Epilogue of the GEMM kernel
+enum GemmMode {
+  kModeStaging = 0,   // INT8 x INT8 -> bf16 head-major staging (h3s_qkv_gemm_chunk[_norm_rope])
+  kModeCarriers = 1,  // INT8 x INT8 -> carriers (h3s_qkv_gemm_chunk_carriers)
+  kModeDense = 2,     // any operand kind -> scaled, biased, activated bf16 row-major matrix (h3s_dense_gemm)
+};
+
+template <int kMode>
 struct GemmLayout {
+  static constexpr bool kCarriers = kMode != kModeStaging;  // both stage half tiles for coalesced stores
   static constexpr int kStages = kCarriers ? 3 : 4;
   static constexpr uint32_t kOffB = kStages * kGemmABytes;
   static constexpr uint32_t kOffTile = kOffB + kStages * kGemmBBytes;
@@ -183,7 +193,21 @@ struct GemmParams {
   double *k_sum;                   // (heads, 128) running column sums of K, or null
   unsigned int *v_amax_bits;       // (heads, 128) running column maxima of |V| as float bits
   int summary_dtype, sequence_total, row_start;
+  // dense epilogue (h3s_dense_gemm): out[m, n] = act(acc * row_scale[m] * col_scale[n] + bias[n]) as bf16
+  int operand_kind;                // H3S_GEMM_I8 / BF16 / F16 / E4M3
+  const float *row_scale;          // (rows) or null
+  const float *col_scale;          // (n_out) or null
+  const float *bias;               // (n_out) or null
+  int activation;                  // H3S_ACT_NONE / H3S_ACT_GELU_TANH
+  __nv_bfloat16 *dense_out;        // (rows, ldc)
+  int64_t ldc;
 };
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), the formula of torch's approximate='tanh'
+  const float inner = 0.7978845608028654f * __fmaf_rn(0.044715f * x, x * x, x);
+  return 0.5f * x * (1.0f + tanhf(inner));
+}
 
 __device__ __forceinline__ float rope_load(const void *base, int64_t index, int dtype) {
   return dtype == H3S_F32 ? __ldg(static_cast<const float *>(base) + index)
@@ -296,14 +320,15 @@ __device__ __forceinline__ void norm_rope_row(uint32_t (&y)[H3S_HEAD_DIM / 2], c
   }
 }
 
-template <bool kCarriers>
+template <int kMode>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const GemmParams prm) {
   extern __shared__ unsigned char smem_dyn[];
   unsigned char *smem = reinterpret_cast<unsigned char *>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~static_cast<uintptr_t>(1023));
-  using L = GemmLayout<kCarriers>;
+  using L = GemmLayout<kMode>;
+  constexpr bool kCarriers = kMode == kModeCarriers;
   GemmShared &sh = *reinterpret_cast<GemmShared *>(smem + L::kOffBar);
   volatile int *abort_word = &sh.abort_word;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -353,7 +378,12 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::umma_idesc(2, 1, 1, kGemmM, kGemmN);
+      // every kind consumes 32 bytes of K per instruction: four instructions per 128-byte stage
+      const int kind = kMode == kModeDense ? prm.operand_kind : H3S_GEMM_I8;
+      const uint32_t idesc = kind == H3S_GEMM_I8     ? ptx::umma_idesc(2, 1, 1, kGemmM, kGemmN)
+                             : kind == H3S_GEMM_E4M3 ? ptx::umma_idesc(1, 0, 0, kGemmM, kGemmN)
+                             : kind == H3S_GEMM_BF16 ? ptx::umma_idesc(1, 1, 1, kGemmM, kGemmN)
+                                                     : ptx::umma_idesc(1, 0, 0, kGemmM, kGemmN);
       uint32_t it = 0, local = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++local) {
@@ -369,9 +399,19 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint64_t a_desc = ptx::umma_desc_kmajor(ptx::smem_u32(smem + s * kGemmABytes), 1024, ptx::kSwizzle128);
           const uint64_t b_desc =
               ptx::umma_desc_kmajor(ptx::smem_u32(smem + L::kOffB + s * kGemmBBytes), 1024, ptx::kSwizzle128);
+          if (kind == H3S_GEMM_I8) {
 #pragma unroll
-          for (int k = 0; k < kGemmK / 32; ++k)
-            ptx::umma_i8(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < kGemmK / 32; ++k)
+              ptx::umma_i8(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          } else if (kind == H3S_GEMM_E4M3) {
+#pragma unroll
+            for (int k = 0; k < kGemmK / 32; ++k)
+              ptx::umma_f8(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < kGemmK / 32; ++k)
+              ptx::umma_f16(tmem_base + a * kGemmN, a_desc + 2 * k, b_desc + 2 * k, idesc, (ks > 0 || k > 0) ? 1u : 0u);
+          }
           ptx::tc_commit(&sh.empty[s]);
         }
         if (ok) ptx::tc_commit(&sh.acc_full[a]);
@@ -396,12 +436,84 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       ptx::tc_fence_after();
       const int row = tm * kGemmM + quarter * 32 + lane;
       const bool row_ok = row < prm.rows;
-      const float xs = row_ok ? __ldg(prm.x_scale + row) : 0.f;
+      const float xs = prm.x_scale == nullptr ? 1.0f : (row_ok ? __ldg(prm.x_scale + row) : 0.f);
       {
         const int group_col0 = tn * kGemmN + gi * H3S_HEAD_DIM;
         const int group = group_col0 >> 7;  // 128-column group == (kind, head)
         const bool group_ok = group_col0 < prm.n_out;
         const bool normed = prm.q_norm != nullptr && group < 2 * prm.heads;
+        if (kMode == kModeDense) {
+          // ---- dense epilogue: scaled, biased, activated bf16 rows, staged for coalesced stores ----
+          unsigned char *tile = smem + L::kOffTile + gi * kEpilogueTileBytes;
+          const int local_row = quarter * 32 + lane;
+          const float rs = xs;  // row_scale[row], 1 without row scales
+          const bool integer = prm.operand_kind == H3S_GEMM_I8;
+          uint4 *my_row = reinterpret_cast<uint4 *>(tile + local_row * (H3S_HEAD_DIM * 2));
+#pragma unroll 1
+          for (int cc = 0; cc < H3S_HEAD_DIM / 32; ++cc) {
+            uint32_t acc[32];
+            H3S_TMEM_LD32(tmem_base + lane_addr + a * kGemmN + gi * H3S_HEAD_DIM + cc * 32, acc);
+            ptx::tmem_wait_ld();
+            uint32_t y[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              float v[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int col = group_col0 + cc * 32 + i + e;
+                const bool col_ok = col < prm.n_out;
+                float value = integer ? static_cast<float>(static_cast<int>(acc[i + e])) : __uint_as_float(acc[i + e]);
+                const float cs = (prm.col_scale != nullptr && col_ok) ? __ldg(prm.col_scale + col) : 1.0f;
+                value = __fmul_rn(value, __fmul_rn(rs, cs));
+                if (prm.bias != nullptr && col_ok) value = __fadd_rn(value, __ldg(prm.bias + col));
+                if (prm.activation == H3S_ACT_GELU_TANH) value = gelu_tanh(value);
+                v[e] = value;
+              }
+              y[i >> 1] = pack_bf16x2(v[0], v[1]);
+            }
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4)
+              my_row[(cc * 4 + c4) ^ (local_row & 15)] = make_uint4(y[4 * c4], y[4 * c4 + 1], y[4 * c4 + 2], y[4 * c4 + 3]);
+          }
+          // the accumulator has been read: the MMA warp may refill it
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&sh.acc_empty[a]);
+          if (!group_ok) continue;  // the same for the four warps of this half
+          if (lane == 0) ptx::mbar_arrive(&sh.tile_ready[gi]);
+          {
+            const bool got = ptx::mbar_wait(&sh.tile_ready[gi], exchanges & 1u, abort_word, kGemmAbortTile,
+                                            prm.wait_budget_ns);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+          }
+          // 16 threads per row, 16 bytes each: a warp writes two rows of 256 contiguous bytes
+          const int g = quarter * 32 + lane, slot = g >> 4, c = g & 15;
+          uint4 raw[16];
+#pragma unroll
+          for (int p = 0; p < 16; ++p) {
+            const int r = p * 8 + slot;
+            raw[p] = *reinterpret_cast<const uint4 *>(tile + r * (H3S_HEAD_DIM * 2) + ((c ^ (r & 15)) << 4));
+          }
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(&sh.exchange_ready[gi]);
+          {
+            const bool got = ptx::mbar_wait(&sh.exchange_ready[gi], exchanges & 1u, abort_word, kGemmAbortExchange,
+                                            prm.wait_budget_ns);
+            if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+            ++exchanges;
+          }
+          const int valid = min(kGemmM, prm.rows - tm * kGemmM);
+          const int col = group_col0 + c * 8;
+          if (col < prm.n_out) {  // n_out is a multiple of 8: a 16-byte chunk is inside or outside as a whole
+            __nv_bfloat16 *dst = prm.dense_out + static_cast<int64_t>(tm) * kGemmM * prm.ldc + col;
+#pragma unroll
+            for (int p = 0; p < 16; ++p) {
+              const int r = p * 8 + slot;
+              if (r < valid) *reinterpret_cast<uint4 *>(dst + static_cast<int64_t>(r) * prm.ldc) = raw[p];
+            }
+          }
+          continue;  // acc_empty was signalled above
+        }
         if (kCarriers) {
           // ---- carriers straight from the accumulators ----
           // Phase A, one thread per row: de-quantise the row of this head to bf16
@@ -550,7 +662,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 if (r < valid) quantise8<true>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
               }
             } else {
-#pragma unroll 1
+#pragma unroll
               for (int p = 0; p < 16; ++p) {
                 const int r = p * 8 + slot;
                 if (r < valid) quantise8<false>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
@@ -580,7 +692,7 @@ qkv_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (r < valid) quantise8<true>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
                   }
                 } else {
-#pragma unroll 1
+#pragma unroll
                   for (int p = 8 * h; p < 8 * h + 8; ++p) {
                     const int r = p * 8 + slot;
                     if (r < valid) quantise8<false>(raw[p], by_scale, dst + static_cast<int64_t>(r) * H3S_HEAD_DIM);
@@ -791,6 +903,8 @@ static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const i
   prm.q8 = prm.k8 = nullptr; prm.q_scale = prm.k_scale = nullptr; prm.q_summary = prm.k_summary = nullptr;
   prm.k_stage = prm.v_stage = nullptr; prm.k_sum = nullptr; prm.v_amax_bits = nullptr;
   prm.summary_dtype = H3S_F32; prm.sequence_total = rows; prm.row_start = 0;
+  prm.operand_kind = H3S_GEMM_I8; prm.row_scale = nullptr; prm.col_scale = nullptr; prm.bias = nullptr;
+  prm.activation = H3S_ACT_NONE; prm.dense_out = nullptr; prm.ldc = 0;
   if (carriers != nullptr) {
     const h3s_qkv_carriers &c = *carriers;
     prm.q8 = c.q8; prm.k8 = c.k8; prm.q_scale = c.q_scale; prm.k_scale = c.k_scale;
@@ -808,13 +922,13 @@ static int qkv_gemm_chunk_impl(const int8_t *x_i8, const float *x_scale, const i
   const int tiles = prm.m_tiles * prm.n_tiles;
   const int grid = tiles < sms ? tiles : sms;
   if (carriers != nullptr) {
-    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(GemmLayout<true>::kBytes)));
-    qkv_gemm_kernel<true><<<grid, kGemmThreads, GemmLayout<true>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<kModeCarriers>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(GemmLayout<kModeCarriers>::kBytes)));
+    qkv_gemm_kernel<kModeCarriers><<<grid, kGemmThreads, GemmLayout<kModeCarriers>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
   } else {
-    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(GemmLayout<false>::kBytes)));
-    qkv_gemm_kernel<false><<<grid, kGemmThreads, GemmLayout<false>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+    H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<kModeStaging>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(GemmLayout<kModeStaging>::kBytes)));
+    qkv_gemm_kernel<kModeStaging><<<grid, kGemmThreads, GemmLayout<kModeStaging>::kBytes, static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
   }
   H3S_CHECK_CUDA(cudaGetLastError());
   return H3S_OK;
@@ -836,6 +950,48 @@ int h3s_qkv_gemm_chunk_norm_rope(const int8_t *x_i8, const float *x_scale, const
   return qkv_gemm_chunk_impl(x_i8, x_scale, w_i8, w_scale, rows, hidden, 3 * heads * H3S_HEAD_DIM, out_bf16,
                              out_stride_head, q_norm, k_norm, epsilon, rope, rope_dtype, rope_strides, heads, status,
                              stream, "qkv_gemm_chunk_norm_rope");
+}
+
+int h3s_dense_gemm(const void *a, int64_t lda_bytes, const void *b, int64_t ldb_bytes, int operand_kind, int rows,
+                   int n_out, int k_bytes, const float *row_scale, const float *col_scale, const float *bias,
+                   int activation, void *out_bf16, int64_t ldc, int32_t *status, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(a != nullptr && b != nullptr && out_bf16 != nullptr, "dense_gemm: NULL pointer");
+  H3S_CHECK_ARG(operand_kind >= H3S_GEMM_I8 && operand_kind <= H3S_GEMM_E4M3, "dense_gemm: unknown operand kind %d", operand_kind);
+  H3S_CHECK_ARG(activation == H3S_ACT_NONE || activation == H3S_ACT_GELU_TANH, "dense_gemm: unknown activation %d", activation);
+  H3S_CHECK_ARG(rows > 0 && n_out > 0 && n_out % 8 == 0, "dense_gemm: rows %d, n_out %d (a positive multiple of 8)", rows, n_out);
+  H3S_CHECK_ARG(k_bytes > 0 && k_bytes % kGemmK == 0, "dense_gemm: the reduction length %d bytes must be a positive multiple of 128", k_bytes);
+  H3S_CHECK_ARG(lda_bytes >= k_bytes && ldb_bytes >= k_bytes && lda_bytes % 16 == 0 && ldb_bytes % 16 == 0,
+                "dense_gemm: operand row strides must be multiples of 16 bytes and cover the reduction length");
+  H3S_CHECK_ARG(ldc >= n_out && ldc % 8 == 0, "dense_gemm: ldc %lld must be a multiple of 8 and at least n_out", static_cast<long long>(ldc));
+  H3S_CHECK_ARG(((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out_bf16)) & 15) == 0,
+                "dense_gemm: operands and output must be 16-byte aligned");
+  const int cap = h3s_device_capability();
+  if (cap < 0) return cap;
+  if (cap / 10 != 10) return fail(H3S_EARCH, "dense_gemm: needs an sm_100 device, found sm_%d", cap);
+  CUtensorMap ma, mb;
+  int rc = make_tensor_map_u8_2d(&ma, a, k_bytes, rows, lda_bytes, kGemmK, kGemmM, "dense_gemm A map");
+  if (rc) return rc;
+  rc = make_tensor_map_u8_2d(&mb, b, k_bytes, n_out, ldb_bytes, kGemmK, kGemmN, "dense_gemm B map");
+  if (rc) return rc;
+  GemmParams prm;
+  memset(&prm, 0, sizeof(prm));
+  prm.x_scale = row_scale; prm.status = status;
+  prm.rows = rows; prm.n_out = n_out; prm.hidden = k_bytes;
+  prm.m_tiles = ceil_div(rows, kGemmM); prm.n_tiles = ceil_div(n_out, kGemmN); prm.n_step = 1;
+  prm.heads = 1; prm.wait_budget_ns = wait_budget_ns();
+  prm.operand_kind = operand_kind; prm.row_scale = row_scale; prm.col_scale = col_scale; prm.bias = bias;
+  prm.activation = activation; prm.dense_out = static_cast<__nv_bfloat16 *>(out_bf16); prm.ldc = ldc;
+  int device = 0, sms = 0;
+  H3S_CHECK_CUDA(cudaGetDevice(&device));
+  H3S_CHECK_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  H3S_CHECK_CUDA(cudaFuncSetAttribute(qkv_gemm_kernel<kModeDense>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(GemmLayout<kModeDense>::kBytes)));
+  const int tiles = prm.m_tiles * prm.n_tiles;
+  qkv_gemm_kernel<kModeDense><<<tiles < sms ? tiles : sms, kGemmThreads, GemmLayout<kModeDense>::kBytes,
+                               static_cast<cudaStream_t>(stream)>>>(ma, mb, prm);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
 }
 
 int h3s_qkv_gemm_chunk_carriers(const int8_t *x_i8, const float *x_scale, const int8_t *w_i8,

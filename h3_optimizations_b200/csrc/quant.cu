@@ -316,6 +316,67 @@ quant_v_fp8_kernel(const T *__restrict__ v, int64_t stride_h, int64_t stride_s,
 }
 
 // ---------------------------------------------------------------------------
+// Per-row FP8-E4M3 quantisation of a bf16 matrix (activations of the FP8 MLP).
+// One CTA = one row, kept in registers between the amax reduction and the store.
+// ---------------------------------------------------------------------------
+
+constexpr int kRowQuantThreads = 256;
+constexpr int kRowQuantMaxChunks = 8;  // 16-byte loads per thread: rows of up to 16384 channels
+
+__global__ void __launch_bounds__(kRowQuantThreads)
+quant_rows_fp8_kernel(const __nv_bfloat16 *__restrict__ x, int64_t stride_row, int rows, int channels,
+                      uint8_t *__restrict__ out, float *__restrict__ row_scale) {
+  __shared__ float warp_amax[kRowQuantThreads / 32];
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const __nv_bfloat16 *src = x + row * stride_row;
+    Elem<__nv_bfloat16>::Raw raw[kRowQuantMaxChunks];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowQuantMaxChunks; ++i) {
+      const int c0 = (i * kRowQuantThreads + threadIdx.x) * 8;
+      raw[i] = c0 < channels ? Elem<__nv_bfloat16>::load_raw(src + c0) : Elem<__nv_bfloat16>::zero_raw();
+      float v[8];
+      Elem<__nv_bfloat16>::unpack(raw[i], v);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(v[e]));
+    }
+    amax = warp_max(amax);
+    __syncthreads();  // the previous row's readers are done
+    if ((threadIdx.x & 31) == 0) warp_amax[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = warp_amax[0];
+#pragma unroll
+    for (int w = 1; w < kRowQuantThreads / 32; ++w) amax = fmaxf(amax, warp_amax[w]);
+    const float scale = fmaxf(__fdiv_rn(amax, 448.0f), 1.0e-20f);
+    if (threadIdx.x == 0) row_scale[row] = scale;
+    const SharedDivisor by_scale = make_divisor(scale);
+    auto emit = [&](auto exact_tag) {
+      constexpr bool kExact = decltype(exact_tag)::value;
+#pragma unroll
+      for (int i = 0; i < kRowQuantMaxChunks; ++i) {
+        const int c0 = (i * kRowQuantThreads + threadIdx.x) * 8;
+        if (c0 < channels) {
+          float v[8];
+          Elem<__nv_bfloat16>::unpack(raw[i], v);
+          uint32_t word[2];
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            uint16_t lo, hi;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo)
+                : "f"(divide<kExact>(by_scale, v[4 * w + 1])), "f"(divide<kExact>(by_scale, v[4 * w])));
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi)
+                : "f"(divide<kExact>(by_scale, v[4 * w + 3])), "f"(divide<kExact>(by_scale, v[4 * w + 2])));
+            word[w] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+          }
+          *reinterpret_cast<uint2 *>(out + static_cast<int64_t>(row) * channels + c0) = make_uint2(word[0], word[1]);
+        }
+      }
+    };
+    if (by_scale.exact) emit(std::true_type{}); else emit(std::false_type{});
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
 
@@ -447,6 +508,23 @@ int h3s_column_stats(const void *k, int64_t k_stride_h, int64_t k_stride_s, cons
     case H3S_BF16: return launch_column_stats<__nv_bfloat16>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
     default: return launch_column_stats<__half>(k, k_stride_h, k_stride_s, v, v_stride_h, v_stride_s, heads, sequence, v_bound, k_mean, v_scale, scratch, s);
   }
+}
+
+int h3s_quant_rows_fp8(const void *x_bf16, int64_t x_stride_row, int rows, int channels, uint8_t *out,
+                       float *row_scale, h3s_stream_t stream) {
+  using namespace h3s;
+  H3S_CHECK_ARG(x_bf16 != nullptr && out != nullptr && row_scale != nullptr, "quant_rows_fp8: NULL pointer");
+  H3S_CHECK_ARG(rows > 0 && channels > 0 && channels % 8 == 0 && channels <= kRowQuantThreads * 8 * kRowQuantMaxChunks,
+                "quant_rows_fp8: channels %d must be a multiple of 8 and at most %d", channels,
+                kRowQuantThreads * 8 * kRowQuantMaxChunks);
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0 && x_stride_row % 8 == 0 && x_stride_row >= channels,
+                "quant_rows_fp8: input must be 16-byte aligned with a row stride that is a multiple of 8");
+  H3S_CHECK_ARG((reinterpret_cast<uintptr_t>(out) & 7) == 0, "quant_rows_fp8: output must be 8-byte aligned");
+  const int grid = rows < 148 * 8 ? rows : 148 * 8;
+  quant_rows_fp8_kernel<<<grid, kRowQuantThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16 *>(x_bf16), x_stride_row, rows, channels, out, row_scale);
+  H3S_CHECK_CUDA(cudaGetLastError());
+  return H3S_OK;
 }
 
 int h3s_column_stats_finalize(const void *stats, int dtype, int heads, int sequence, float v_bound,

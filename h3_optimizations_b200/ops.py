@@ -370,6 +370,59 @@ def qkv_gemm_chunk_carriers(x_i8, x_scale, w_i8, w_scale, *, heads, row_start, q
     )
 
 
+GEMM_KINDS = {torch.int8: 0, torch.bfloat16: 1, torch.float16: 2, torch.float8_e4m3fn: 3}
+ACT_NONE, ACT_GELU_TANH = 0, 1
+
+
+def dense_gemm(a, b, *, row_scale=None, col_scale=None, bias=None, activation="none", out=None, status=None):
+    """``out = bf16(act((a @ b.T) * row_scale[:, None] * col_scale[None, :] + bias))`` on the
+    tensor cores.  ``a`` (rows, K) and ``b`` (n_out, K) share one element type
+    (int8, bf16, fp16 or float8_e4m3fn) and have contiguous rows; ``b`` is a
+    Linear weight as stored.  ``activation``: ``"none"`` or ``"gelu_tanh"``."""
+    lib = _native.load()
+    if a.ndim != 2 or b.ndim != 2 or a.shape[1] != b.shape[1] or a.dtype != b.dtype or a.dtype not in GEMM_KINDS:
+        raise _native.NativeError("dense_gemm: a (rows, K) and b (n_out, K) must share K and an int8/bf16/fp16/e4m3 type")
+    if not (a.is_cuda and b.is_cuda) or a.stride(1) != 1 or b.stride(1) != 1:
+        raise _native.NativeError("dense_gemm: operands must be CUDA tensors with contiguous rows")
+    rows, k = a.shape
+    n_out = b.shape[0]
+    if out is None:
+        out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=a.device)
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (rows, n_out) or out.stride(1) != 1:
+        raise _native.NativeError("dense_gemm: out must be bf16 (rows, n_out) with contiguous rows")
+    for name, t, n in (("row_scale", row_scale, rows), ("col_scale", col_scale, n_out), ("bias", bias, n_out)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous() or t.device != a.device):
+            raise _native.NativeError("dense_gemm: %s must be a contiguous fp32 tensor of %d elements on the operands' device" % (name, n))
+    act = {"none": ACT_NONE, "gelu_tanh": ACT_GELU_TANH}.get(activation)
+    if act is None:
+        raise _native.NativeError("dense_gemm: activation must be 'none' or 'gelu_tanh'")
+    size = a.element_size()
+    check(
+        lib.h3s_dense_gemm(ptr(a), a.stride(0) * size, ptr(b), b.stride(0) * size, GEMM_KINDS[a.dtype], rows, n_out,
+                           k * size, ptr(row_scale), ptr(col_scale), ptr(bias), act, ptr(out), out.stride(0),
+                           ptr(status), stream_ptr(a.device)),
+        "h3s_dense_gemm",
+    )
+    return out
+
+
+def quant_rows_fp8(x, out=None, row_scale=None):
+    """Per-row FP8-E4M3 of a bf16 matrix: ``(codes e4m3 (rows, C), scale fp32 (rows,))``."""
+    lib = _native.load()
+    if x.ndim != 2 or x.dtype != torch.bfloat16 or not x.is_cuda or x.stride(1) != 1:
+        raise _native.NativeError("quant_rows_fp8: x must be a rank-2 CUDA bf16 tensor with contiguous rows")
+    rows, channels = x.shape
+    if out is None:
+        out = torch.empty((rows, channels), dtype=torch.float8_e4m3fn, device=x.device)
+    if row_scale is None:
+        row_scale = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    if out.shape[0] < rows or out.shape[1] != channels or not out.is_contiguous() or row_scale.numel() < rows:
+        raise _native.NativeError("quant_rows_fp8: output buffers are too small")
+    check(lib.h3s_quant_rows_fp8(ptr(x), x.stride(0), rows, channels, ptr(out), ptr(row_scale), stream_ptr(x.device)),
+          "h3s_quant_rows_fp8")
+    return out[:rows], row_scale[:rows]
+
+
 def route_topk(q_summary, k_summary, *, q_start, q_stop, kv_start, kv_stop, retained):
     """Compact route ``int32 (1,H,q_stop-q_start,route_len)``."""
     lib = _native.load()

@@ -295,6 +295,48 @@ int h3s_column_stats_finalize(const void *stats, int dtype, int heads,
                               int sequence, float v_bound, float *k_mean,
                               float *v_scale, h3s_stream_t stream);
 
+/* Dense GEMM --------------------------------------------------------------- */
+
+#define H3S_GEMM_I8 0    /* int8 x int8, int32 accumulation   */
+#define H3S_GEMM_BF16 1  /* bf16 x bf16, fp32 accumulation    */
+#define H3S_GEMM_F16 2   /* fp16 x fp16, fp32 accumulation    */
+#define H3S_GEMM_E4M3 3  /* e4m3 x e4m3, fp32 accumulation    */
+#define H3S_ACT_NONE 0
+#define H3S_ACT_GELU_TANH 1
+
+/*
+ * out[m, n] = bf16( act( (sum_k a[m,k] * b[n,k]) * row_scale[m] * col_scale[n] + bias[n] ) )
+ * on the tcgen05 tensor cores (the persistent TMA-fed kernel of the QKV
+ * projection with a row-major epilogue whose stores are staged through shared
+ * memory and leave as full lines).
+ *   a        (rows, K) elements of `operand_kind`, row stride lda_bytes
+ *   b        (n_out, K), row stride ldb_bytes: a torch Linear weight as stored
+ *   k_bytes  K * element size, a multiple of 128
+ *   row_scale (rows), col_scale (n_out), bias (n_out): fp32, each may be NULL
+ *   activation H3S_ACT_NONE or H3S_ACT_GELU_TANH (torch's approximate='tanh')
+ *   out_bf16 (rows, ldc) bf16, n_out a multiple of 8
+ * Replaces the attention module's out_proj call behind execute_projected
+ * (attention_forward.py:99-128, attention/sparse/sparse_sage_streamed.py:1454-1472)
+ * and the two FP8 linears of the chunked MLP (memory/linear.py:352-492,
+ * memory/forward.py:138-298).
+ */
+int h3s_dense_gemm(const void *a, int64_t lda_bytes, const void *b,
+                   int64_t ldb_bytes, int operand_kind, int rows, int n_out,
+                   int k_bytes, const float *row_scale, const float *col_scale,
+                   const float *bias, int activation, void *out_bf16,
+                   int64_t ldc, int32_t *status, h3s_stream_t stream);
+
+/*
+ * Per-row FP8-E4M3 quantisation of a bf16 matrix: scale[m] = max(amax_m / 448,
+ * 1e-20), code = e4m3(x / scale[m]).  x (rows, channels) with row stride in
+ * elements, channels a multiple of 8; out (rows, channels) contiguous.
+ * Replaces the activation quantisation in front of the FP8 linears
+ * (memory/linear.py:352-492).
+ */
+int h3s_quant_rows_fp8(const void *x_bf16, int64_t x_stride_row, int rows,
+                       int channels, uint8_t *out, float *row_scale,
+                       h3s_stream_t stream);
+
 /*
  * Upper bound, in nanoseconds, of every wait inside the tcgen05 kernels
  * (attention and QKV GEMM) launched after the call; default 2 s, accepted range

@@ -215,3 +215,42 @@ def test_convrot_rotation_is_orthonormal_and_cancels():
     assert codes.dtype == torch.int8 and int(codes.abs().max()) == 127
     back = codes.float() * scale[:, None]
     assert float((back - (x.to(torch.bfloat16).float().reshape(64, 2, 256) @ rot).reshape(64, 512)).abs().max()) <= float(scale.max()) * 0.5 + 1e-6
+
+
+def test_reference_router_on_bf16_inputs_differs_from_its_fp32_path_only_at_the_cutoff():
+    """The bit-exact mask gate is stated for FP32 inputs (the fixtures above were
+    generated from FP32-widened Q/K, and the CUDA router, which scores in FP64,
+    reproduces them row for row).  In production the reference router sees bf16:
+    it pools to bf16 means and scores with a bf16 matmul, so its scores carry
+    eight significant bits and `torch.topk` breaks the resulting near-ties in an
+    order it does not specify.  This test measures how far the reference's own
+    two paths are apart on the benchmark's inputs: a quarter of the rows differ,
+    each by one or two of its 162 tiles, always around the cutoff score.  A mask
+    that is bit-exact against the bf16 path is therefore not a well-defined
+    target; the FP32 path is."""
+    import dataclasses
+
+    from oracle import ref_bridge
+
+    if not ref_bridge.available():
+        pytest.skip("oracle/_ref is not staged")
+    spec = dataclasses.replace(workloads.CONFIG1, heads=2)
+    q, k, _ = workloads.structured_qkv(spec, seed=0)
+    absolute = ref_bridge.bench_module().absolute_lut
+    lut32, valid32, _ = ref_bridge.build_lut(q.float(), k.float(), spec.sequence, 512, 0.3)
+    lut16, valid16, _ = ref_bridge.build_lut(q, k, spec.sequence, 512, 0.3)
+    assert torch.equal(valid32, valid16)
+    listed = int(valid32[0, 0, -1])
+    rows32 = absolute(torch, lut32)[0, :, 4:, :listed].long()
+    rows16 = absolute(torch, lut16)[0, :, 4:, :listed].long()
+    mask32 = torch.zeros((2, 256, 520), dtype=torch.bool).scatter_(2, rows32, True)
+    mask16 = torch.zeros((2, 256, 520), dtype=torch.bool).scatter_(2, rows16, True)
+    swapped = (mask32 & ~mask16).sum(dim=-1)          # tiles the FP32 path takes and the bf16 path drops
+    differing_rows = int((swapped > 0).sum())
+    print("reference router, bf16 vs fp32 inputs: %d of %d rows differ, %.2f tiles per row on average, at most %d"
+          % (differing_rows, swapped.numel(), float(swapped.float().mean()), int(swapped.max())))
+    assert 0 < differing_rows < 0.5 * swapped.numel()
+    assert int(swapped.max()) <= 4 and float(swapped.float().mean()) < 1.0
+    # and the oracle (FP32 scoring, as the CUDA router is tested against) equals the FP32 path
+    _, _, _, route = oracle.build_route(q.float(), k.float(), spec.sequence, 512, 0.3)
+    assert torch.equal(route[0].long(), rows32)
