@@ -275,6 +275,26 @@ def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4, keep=False):
     return result
 
 
+class quiet_host:
+    """Timed regions run with the cyclic garbage collector off (collected once
+    before): at 8 GPUs a step lasts under a millisecond while the host needs a
+    good part of that to queue it, so a collector pause of a few milliseconds
+    would show up as device idle time."""
+
+    def __enter__(self):
+        import gc
+
+        gc.collect()
+        gc.disable()
+        return self
+
+    def __exit__(self, *exc):
+        import gc
+
+        gc.enable()
+        return False
+
+
 class Stdout:
     """stdout carries exactly one JSON line.  Libraries that log to file
     descriptor 1 (NCCL with NCCL_DEBUG=INFO does) are sent to stderr instead, so
@@ -444,15 +464,16 @@ def run_attention(args, spec, stdout):
     sampler.mark_begin()
     t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
-    t_begin.record()
     out = None
     sparse_by_position = {}
     calls = args.steps * len(positions)
-    for i in range(calls):
-        out, sparse = step(i % len(positions), record=True)
-        sparse_by_position.setdefault(i % len(positions), sparse)
-    t_end.record()
-    fence()
+    with quiet_host():
+        t_begin.record()
+        for i in range(calls):
+            out, sparse = step(i % len(positions), record=True)
+            sparse_by_position.setdefault(i % len(positions), sparse)
+        t_end.record()
+        fence()
     region_seconds = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
     device_ms = t_begin.elapsed_time(t_end) / calls
@@ -497,11 +518,12 @@ def run_attention(args, spec, stdout):
             e2e_step(i)
         fence()
         b0 = torch.cuda.Event(enable_timing=True); b1 = torch.cuda.Event(enable_timing=True)
-        b0.record()
-        for i in range(e2e_calls):
-            e2e_step(i)
-        b1.record()
-        fence()
+        with quiet_host():
+            b0.record()
+            for i in range(e2e_calls):
+                e2e_step(i)
+            b1.record()
+            fence()
         e2e_ms = torch.tensor([b0.elapsed_time(b1) / e2e_calls], dtype=torch.float64, device=device)
         moved = torch.tensor([3.0 * q_host.numel() * q_host.element_size(),
                               float(out_host.numel() * out_host.element_size())], dtype=torch.float64, device=device)
@@ -636,10 +658,11 @@ def run_config2(args, spec, stdout):
     sampler.mark_begin()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
-    t0.record()
-    for _ in range(args.steps):
-        _, sparse = step(record=True)
-    t1.record(); fence()
+    with quiet_host():
+        t0.record()
+        for _ in range(args.steps):
+            _, sparse = step(record=True)
+        t1.record(); fence()
     region_seconds = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
     step_ms = t0.elapsed_time(t1) / args.steps
@@ -793,10 +816,11 @@ def run_config4(args, spec, stdout):
     sampler.mark_begin()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     wall0 = time.perf_counter()
-    t0.record()
-    for _ in range(args.steps):
-        _, sparse = step(record=True)
-    t1.record(); fence()
+    with quiet_host():
+        t0.record()
+        for _ in range(args.steps):
+            _, sparse = step(record=True)
+        t1.record(); fence()
     region_seconds = time.perf_counter() - wall0
     clocks = sampler.stop() if rank == 0 else None
     stage = [statistics.mean(m[i].elapsed_time(m[i + 1]) for m in marks) for i in range(4)]

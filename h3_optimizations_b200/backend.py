@@ -260,7 +260,10 @@ class B200SparseBackend:
             side = self._side_stream(q.device)
             k_mean, v_scale, scratch = ops.column_stats_buffers(heads, q.device, want_k_mean=self.smooth_k)
             v_carrier = ops.allocate_v_carrier(sequence, heads, v.device)
-            stats_done = torch.cuda.Event()
+            events = self.__dict__.setdefault("_stats_events", {})
+            stats_done = events.get(side)
+            if stats_done is None:
+                stats_done = events[side] = torch.cuda.Event()
             side.wait_stream(main)
             try:
                 with torch.cuda.stream(side):
