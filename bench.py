@@ -395,6 +395,57 @@ def tensor_roofline(kernel, achieved_tops, peaks, peak_source, region_seconds, t
     }
 
 
+def projection_summary(spec, device, steps=3):
+    """The chunked QKV projection of the same layer on one GPU, timed briefly so that
+    the default benchmark line also carries the projection's figures: hidden 3072 ->
+    3 x 24 x 128, 4096-token chunks, carriers from the GEMM epilogue."""
+    from types import SimpleNamespace
+
+    from h3_optimizations_b200 import ChunkedSparseQKVProjector, ops
+
+    hidden = 3072
+    x, w, w_scale = workloads.projection_inputs(spec.sequence, hidden=hidden, heads=spec.heads, seed=0)
+    x, w, w_scale = x.to(device), w.to(device), w_scale.to(device)
+    module = SimpleNamespace(heads=spec.heads, head_dim=HEAD_DIM, qkv_weight_int8=w, qkv_weight_scale=w_scale)
+    projector = ChunkedSparseQKVProjector()
+
+    def timed(fn):
+        for _ in range(2): fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps): fn()
+        e1.record(); torch.cuda.synchronize(device)
+        return e0.elapsed_time(e1) / steps
+
+    project_ms = timed(lambda: projector.project(module, x, None, layer_index=0, transformer_options={}))
+    chunks = [(a, min(a + 4096, spec.sequence)) for a in range(0, spec.sequence, 4096)]
+    x_i8, x_scale = ops.convrot_quant_rows(x)
+    shape = (1, spec.heads, spec.sequence, HEAD_DIM)
+    q8 = torch.empty(shape, dtype=torch.int8, device=device)
+    qs = torch.empty((1, spec.heads, (spec.sequence + 127) // 128), device=device)
+    qsum = torch.empty((1, spec.heads, (spec.sequence + 127) // 128, HEAD_DIM), device=device)
+    ksum = torch.empty((1, spec.heads, (spec.sequence + 63) // 64, HEAD_DIM), device=device)
+    v_stage = torch.empty(shape, dtype=torch.bfloat16, device=device)
+    k_stage = torch.empty_like(v_stage)
+    stats = ops.column_stats_scratch(spec.heads, device)
+
+    def gemm():
+        for a, b in chunks:
+            ops.qkv_gemm_chunk_carriers(x_i8[a:b], x_scale[a:b], w, w_scale, heads=spec.heads, row_start=a, q_int8=q8,
+                                        q_scale=qs, q_summary=qsum, k_summary=ksum, v_stage=v_stage, stats=stats,
+                                        k_stage=k_stage)
+
+    gemm_ms = timed(gemm)
+    gemm_ops = 2.0 * spec.sequence * hidden * 3 * spec.heads * HEAD_DIM
+    peaks, _ = measured_peaks()
+    tops = gemm_ops / (gemm_ms * 1e-3) / 1e12
+    return {"workload": "x (%d,%d) bf16 -> ConvRot INT8 QKV projection (W %dx%d int8), 4096-token chunks, carriers from the "
+                        "GEMM epilogue" % (spec.sequence, hidden, 3 * spec.heads * HEAD_DIM, hidden),
+            "projection_ms": project_ms, "qkv_gemm_all_chunks_ms": gemm_ms, "qkv_gemm_ops": gemm_ops,
+            "qkv_gemm_tops": tops, "frac_of_burst": tops / (2.0 * float(peaks["bf16_tflops"])),
+            "frac_of_nominal_4500": tops / NOMINAL_INT8_TOPS, "gpu_launches_per_projection": len(chunks) * 2 + 4}
+
+
 def run_attention(args, spec, stdout):
     """The headline workload (and the 76112-token one): carriers -> router ->
     attention (-> exchange) on N GPUs through the backend objects."""
@@ -571,6 +622,8 @@ def run_attention(args, spec, stdout):
                                                   "(profiles/), scaled to the %d heads of one launch" % heads_local)
         if schedule is not None:
             line["schedule_ms"] = schedule
+        if world == 1 and spec.sequence == 33272 and not args.heads and not args.schedule and not args.skip_e2e:
+            line["qkv_projection"] = projection_summary(spec, device)
         if e2e is not None:
             line["e2e"] = e2e
         if world == 1 and not args.skip_cpu_baseline:

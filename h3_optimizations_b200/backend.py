@@ -413,7 +413,7 @@ class B200SparseBackend:
 
     # -- host-resident activations -------------------------------------------
 
-    def forward_host(self, q, k, v, out=None, *, layer_index, transformer_options, heads_per_chunk=2):
+    def forward_host(self, q, k, v, out=None, *, layer_index, transformer_options, heads_per_chunk=None):
         """``prepare`` + ``execute`` for Q/K/V that live in (pinned) HOST memory.
 
         Heads are independent on the whole path, so the call walks the heads in
@@ -440,6 +440,9 @@ class B200SparseBackend:
             raise SparseSageError("forward_host: out must be a contiguous host tensor shaped and typed like q")
         recorder = (transformer_options or {}).get("h3_optimizations_attention_route")
         whole = getattr(recorder, "sink", None) is not None
+        if heads_per_chunk is None:
+            # at least four chunks when the heads allow it, so that copy-in, kernels and copy-out overlap
+            heads_per_chunk = 2 if heads >= 8 else 1
         chunk = heads if whole else max(1, min(int(heads_per_chunk), heads))
         bounds = [(a, min(a + chunk, heads)) for a in range(0, heads, chunk)]
         device = torch.device("cuda", torch.cuda.current_device())

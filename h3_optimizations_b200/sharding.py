@@ -238,7 +238,7 @@ class HeadShardedBackend:
         dist.all_reduce(same, op=dist.ReduceOp.MIN, group=self.group)
         return bool(int(same.item()))
 
-    def forward_host(self, q, k, v, out=None, *, layer_index, transformer_options, heads_per_chunk=2):
+    def forward_host(self, q, k, v, out=None, *, layer_index, transformer_options, heads_per_chunk=None):
         """Host-resident entry of this rank's heads: Q/K/V ``(1, h_local, S, 128)``
         in (pinned) host memory in, the matching output slice out, copies and
         kernels pipelined over three streams.  No exchange: across the ranks the
