@@ -54,9 +54,16 @@ convrot_quant_rows_kernel(const __nv_bfloat16 *__restrict__ x, int64_t x_stride,
   extern __shared__ float warp_amax[];  // one per warp
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int groups = hidden / kRotGroup;  // == warps per CTA
+  // the next row's 16 bytes are requested before this row is transformed, so every
+  // thread keeps two loads in flight across the row's two barriers
+  const __nv_bfloat16 *column = x + warp * kRotGroup + lane * 8;
+  Elem<__nv_bfloat16>::Raw ahead = blockIdx.x < rows ? Elem<__nv_bfloat16>::load_raw(column + blockIdx.x * x_stride)
+                                                     : Elem<__nv_bfloat16>::zero_raw();
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     float v[8];
-    Elem<__nv_bfloat16>::load8(x + row * x_stride + warp * kRotGroup + lane * 8, v);
+    Elem<__nv_bfloat16>::unpack(ahead, v);
+    const int next = row + gridDim.x;
+    if (next < rows) ahead = Elem<__nv_bfloat16>::load_raw(column + static_cast<int64_t>(next) * x_stride);
     fwht8(v);
 #pragma unroll
     for (int bit = 0; bit < 5; ++bit) {
