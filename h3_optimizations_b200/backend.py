@@ -250,29 +250,37 @@ class B200SparseBackend:
             retained = self.router._retained(video_budget, geometry)
             need_route = retained < geometry.pure_video_kv_tiles
             summary_dtype = torch.float64 if need_route else None
-            # Three chains share the GPU: the column statistics (K mean, V scale) and the V
-            # carrier that needs them run on a second stream; the Q quantiser, which needs
-            # neither, starts at once on the current one; the K quantiser joins when the
-            # statistics are in.  Each of these kernels alone leaves half of the memory
-            # system idle, and the router behind them is latency bound.  Every buffer is
-            # allocated on the current stream, which both chains rejoin before returning.
+            # Two streams share the GPU.  The column statistics (K mean, V scale) run on a
+            # second stream while the Q quantiser, which needs neither, starts at once on the
+            # current one; the K quantiser joins when the statistics are in.  The V carrier
+            # is held back until the K quantiser is through, so that this memory-bound
+            # kernel runs beside the router, which is latency bound and leaves the memory
+            # system idle, instead of sharing the bandwidth with the K quantiser.  Every
+            # buffer is allocated on the current stream, which both chains rejoin before
+            # returning.
             main = torch.cuda.current_stream(q.device)
             side = self._side_stream(q.device)
             k_mean, v_scale, scratch = ops.column_stats_buffers(heads, q.device, want_k_mean=self.smooth_k)
             v_carrier = ops.allocate_v_carrier(sequence, heads, v.device)
             events = self.__dict__.setdefault("_stats_events", {})
-            stats_done = events.get(side)
-            if stats_done is None:
-                stats_done = events[side] = torch.cuda.Event()
+            pair = events.get(side)
+            if pair is None:
+                pair = events[side] = (torch.cuda.Event(), torch.cuda.Event())
+            stats_done, k_done = pair
             side.wait_stream(main)
             try:
                 with torch.cuda.stream(side):
                     ops.column_stats_into(k if self.smooth_k else None, v, k_mean, v_scale, scratch, V_QUANT_BOUND)
                     stats_done.record(side)
-                    ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
                 q_int8, q_scale, q_summary = ops.quant_qk_blocks(q, Q_TILE, summary_dtype=summary_dtype)
                 main.wait_event(stats_done)
                 k_int8, k_scale, k_summary = ops.quant_qk_blocks(k, KV_TILE, mean=k_mean, summary_dtype=summary_dtype)
+                if need_route:
+                    k_done.record(main)
+                with torch.cuda.stream(side):
+                    if need_route:
+                        side.wait_event(k_done)
+                    ops.quant_v_fp8_into(v, v_scale, v_carrier, v_bound=V_QUANT_BOUND)
                 if need_route:
                     route = self.router.build_route_from_summaries(
                         q_summary, k_summary, snapshot.layout, video_budget,
