@@ -275,6 +275,35 @@ def cpu_reference_sample(spec, budget, steps=1, warmup=0, heads=4, keep=False):
     return result
 
 
+
+WARM_SECONDS = 0.3
+
+
+def warm_up(step, count, world):
+    """`count` untimed steps, then more until every rank has kept its GPU busy for
+    WARM_SECONDS: a GPU that sat idle while the smaller runs of a scaling series
+    used its neighbours starts at idle clocks, and the max over ranks would time
+    its ramp instead of the kernels.  Every rank runs the same number of steps
+    (the exchange inside a step is collective), agreed on through one all-reduce."""
+    import torch
+    import torch.distributed as dist
+
+    count = max(1, count)
+    begin = time.perf_counter()
+    for i in range(count):
+        result = step(i)
+    torch.cuda.synchronize()
+    per_step = max((time.perf_counter() - begin) / count, 1e-5)
+    extra = int(max(0.0, WARM_SECONDS - (time.perf_counter() - begin)) / per_step)
+    if world > 1:
+        agreed = torch.tensor([extra], dtype=torch.int64, device="cuda")
+        dist.all_reduce(agreed, op=dist.ReduceOp.MAX)
+        extra = int(agreed.item())
+    for i in range(min(extra, 2000)):
+        result = step(count + i)
+    return result
+
+
 class quiet_host:
     """Timed regions run with the cyclic garbage collector off (collected once
     before): at 8 GPUs a step lasts under a millisecond while the host needs a
@@ -508,9 +537,7 @@ def run_attention(args, spec, stdout):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    sparse = None
-    for i in range(args.warmup):
-        _, sparse = step(i % len(positions))
+    _, sparse = warm_up(lambda i: step(i % len(positions)), args.warmup, world)
     fence()
     sampler.mark_begin()
     t_begin = torch.cuda.Event(enable_timing=True); t_end = torch.cuda.Event(enable_timing=True)
@@ -537,7 +564,12 @@ def run_attention(args, spec, stdout):
     local_ops = statistics.mean(ops_by_position[p] for p, _ in records)
     attn_ops_rate = statistics.mean(ops_by_position[p] / (e[1].elapsed_time(e[2]) * 1e-3) for p, e in records) / 1e12
     totals = torch.tensor([local_ops, device_ms, attn_ms, prep_ms, exch_ms], dtype=torch.float64, device=device)
+    per_rank = None
     if world > 1:
+        every = [torch.zeros_like(totals) for _ in range(world)]
+        dist.all_gather(every, totals)
+        per_rank = [{"prepare": round(float(t[3]), 4), "attention": round(float(t[2]), 4),
+                     "exchange tail": round(float(t[4]), 4)} for t in every]
         summed = totals.clone(); dist.all_reduce(summed, op=dist.ReduceOp.SUM)
         maxed = totals.clone(); dist.all_reduce(maxed, op=dist.ReduceOp.MAX)
         total_ops, device_ms, attn_ms, prep_ms, exch_ms = (float(summed[0]), float(maxed[1]), float(maxed[2]),
@@ -604,12 +636,16 @@ def run_attention(args, spec, stdout):
             "config": {
                 "workload": workload_name(spec, args.budget) + (" [30-step schedule 0.5,0.5,0.3x26,0.5,0.5]" if args.schedule else ""),
                 "heads_per_gpu": heads_local, "parallelism": "head-sharded x%d" % world, "exchange": exchange,
-                "l2_policy": "inputs (Q,K,V bf16 = %.0f MB per GPU) exceed the 126 MB L2; no flush"
-                             % (heads_local * spec.sequence * HEAD_DIM * 2 * 3 / 1e6),
+                "l2_policy": "no flush: a step streams %.0f MB of bf16 Q/K/V, %.0f MB of carriers (written, then read) and "
+                             "the %.0f MB gathered output through this GPU's 126 MB L2"
+                             % (heads_local * spec.sequence * HEAD_DIM * 2 * 3 / 1e6,
+                                heads_local * spec.sequence * HEAD_DIM * 3 / 1e6,
+                                spec.heads * spec.sequence * HEAD_DIM * 2 / 1e6),
                 "p_terms": 2, "algorithmic_ops": total_ops, "route_len": sparse.route.route_len,
                 "layer_calls_per_step": len(positions),
             },
             "stages_ms": {"prepare (stats+quant+route)": prep_ms, "attention": attn_ms, "exchange tail": exch_ms},
+            "stages_ms_per_rank": per_rank,
             "prepare_hbm": {"bytes": carrier_bytes, "gbs": carrier_bytes / (prep_ms * 1e-3) / 1e9,
                             "frac_of_measured_copy": carrier_bytes / (prep_ms * 1e-3) / 1e9 / float(peaks["hbm_gbs"])},
             "roofline": tensor_roofline("sparse_attn_tc_kernel", attn_ops_rate, peaks, peak_source, region_seconds, traffic),
@@ -704,9 +740,7 @@ def run_config2(args, spec, stdout):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    sparse = None
-    for _ in range(args.warmup):
-        _, sparse = step()
+    _, sparse = warm_up(lambda i: step(), args.warmup, world)
     fence()
     sampler.mark_begin()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -862,9 +896,7 @@ def run_config4(args, spec, stdout):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    sparse = None
-    for _ in range(args.warmup):
-        _, sparse = step()
+    _, sparse = warm_up(lambda i: step(), args.warmup, world)
     fence()
     sampler.mark_begin()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
