@@ -946,8 +946,32 @@ def run_config4(args, spec, stdout):
         dist.destroy_process_group()
 
 
+def pin_rank_cores():
+    """Multi-rank runs: give every rank its own share of the host cores before any
+    thread is started.  At a step of under a millisecond a rank whose launching
+    thread is moved or preempted for 50 us leaves its GPU idle, and the barrier at
+    the end of the step makes every other rank wait for it.  Off unless
+    H3S_BENCH_PIN=1."""
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world <= 1 or os.environ.get("H3S_BENCH_PIN", "0") != "1" or not hasattr(os, "sched_setaffinity"):
+        return None
+    allowed = sorted(os.sched_getaffinity(0))
+    share = len(allowed) // world
+    if share < 1:
+        return None
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    mine = allowed[local * share:(local + 1) * share]
+    try:
+        os.sched_setaffinity(0, mine)
+    except OSError:
+        return None
+    return mine
+
+
 def main():
     args = parse_args()
+    if args.impl != "reference":
+        pin_rank_cores()
     stdout = Stdout()
     spec = {"config1": workloads.CONFIG1, "config2": workloads.CONFIG1, "config3": workloads.CONFIG3,
             "config4": workloads.CONFIG4}[args.config]
