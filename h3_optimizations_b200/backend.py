@@ -51,6 +51,37 @@ def preflight():
     return capability
 
 
+class CapturedLayerCall:
+    """``prepare`` + ``execute`` of one layer call on fixed input tensors, captured
+    once into a CUDA graph.  A sampler calls the same layer with the same shapes
+    and the same budget step after step; replaying the graph takes the host out
+    of the step (about ten launches and a dozen stream operations otherwise) and
+    closes the gaps between the small carrier kernels.  Every kernel still runs on
+    every replay - statistics, carriers, router, attention (and, for a sharded
+    owner, the exchange) - on whatever ``q``, ``k``, ``v`` hold at that moment; the
+    output tensor and the carriers are the same buffers each time.  The device
+    status word is not looked at between replays: call ``check_status()``.
+    """
+
+    def __init__(self, owner, q, k, v, *, layer_index, transformer_options, warmup=2):
+        self.owner = owner
+        # streams, status words, kernel attributes and exchange buffers come into being on the first
+        # calls; none of that may happen inside the capture
+        for _ in range(max(1, int(warmup))):
+            owner.execute(owner.prepare(q, k, v, layer_index=layer_index, transformer_options=transformer_options))
+        torch.cuda.synchronize(q.device)
+        self.graph = torch.cuda.CUDAGraph()
+        # thread-local error mode: a watchdog thread of a communication library may legally touch the
+        # device while this thread captures
+        with torch.cuda.graph(self.graph, capture_error_mode="thread_local"):
+            self.prepared = owner.prepare(q, k, v, layer_index=layer_index, transformer_options=transformer_options)
+            self.out = owner.execute(self.prepared)
+
+    def replay(self):
+        self.graph.replay()
+        return self.out
+
+
 class B200SparseBackend:
     name = "b200_sparse"
     requires_registered_sage = False
@@ -217,6 +248,8 @@ class B200SparseBackend:
 
     def _poll_status(self, device):
         """Non-blocking look at the mirror of the previous launch's status."""
+        if torch.cuda.is_current_stream_capturing():
+            return  # an event query is not allowed inside a capture; check_status() covers replays
         slot = self._status.get(device.index if device.index is not None else torch.cuda.current_device())
         if slot is not None and slot[2].query():
             self._raise_for(slot[1].tolist(), "reported by an earlier launch")
@@ -367,14 +400,21 @@ class B200SparseBackend:
                 q_start=geometry.pure_video_q_start, q_stop=geometry.pure_video_q_stop,
                 out=out, out_dtype=out_dtype, status=word, peer_out_ptrs=peer_out_ptrs,
             )
-            mirror.copy_(word, non_blocking=True)  # 16 bytes, stream ordered behind the kernel
-            copied.record(torch.cuda.current_stream(device))
+            if not torch.cuda.is_current_stream_capturing():
+                # (an event recorded inside a capture could not be queried afterwards: replays are
+                # covered by check_status(), which reads the device word itself)
+                mirror.copy_(word, non_blocking=True)  # 16 bytes, stream ordered behind the kernel
+                copied.record(torch.cuda.current_stream(device))
             return result
         except _native.NativeError as exc:
             raise SparseSageError(
                 "Sparse attention kernel failed: layer=%d sequence=%d heads=%d dtype=%s: %s"
                 % (sparse.layer_index, sparse.sequence, sparse.heads, sparse.output_dtype, exc)
             ) from exc
+
+    def capture(self, q, k, v, *, layer_index, transformer_options):
+        """This layer call as a replayable CUDA graph (see ``CapturedLayerCall``)."""
+        return CapturedLayerCall(self, q, k, v, layer_index=layer_index, transformer_options=transformer_options)
 
     def execute_projected(self, module, prepared):
         """Attention followed by the block's ``out_proj`` on the tensor cores:

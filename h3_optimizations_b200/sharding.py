@@ -224,6 +224,18 @@ class HeadShardedBackend:
             gather_heads(local.clone(), self.heads, self.group, out=self._full)
         return self._full
 
+    def capture(self, q, k, v, *, layer_index, transformer_options):
+        """Local prepare + attention + exchange as a replayable CUDA graph
+        (``backend.CapturedLayerCall``).  Collective: every rank captures, and
+        every rank replays the same number of times."""
+        from .backend import CapturedLayerCall
+
+        if self.exchange is None:  # the ranks agree on the exchange path at the first call
+            self.execute(self.prepare(q, k, v, layer_index=layer_index, transformer_options=transformer_options))
+        if self.exchange != "peer":
+            raise RuntimeError("only the peer-store exchange is captured; with the NCCL all-gather run the step eagerly")
+        return CapturedLayerCall(self, q, k, v, layer_index=layer_index, transformer_options=transformer_options)
+
     def check_exchange(self, prepared):
         """Collective self-check: the reassembled output must equal an NCCL
         all-gather of the local slices bit for bit.  Returns True/False."""

@@ -107,3 +107,29 @@ def test_forward_host_matches_device_path(backend):
     assert torch.equal(again, expected)
     with pytest.raises(Exception, match="host tensors"):
         backend.forward_host(q.cuda(), k.cuda(), v.cuda(), layer_index=0, transformer_options=options)
+
+
+def test_captured_layer_call_replays_every_kernel(backend):
+    """``backend.capture``: prepare + execute as one CUDA graph.  A replay must give
+    the eager result bit for bit, follow the contents of the input tensors (all the
+    kernels run again, nothing is cached), and leave the eager path usable."""
+    from h3_optimizations_b200 import runtime_options
+
+    spec = workloads.small_spec("graph", 2, 192, 832 + 17)
+    q, k, v = (t.cuda() for t in workloads.gaussian_qkv(spec, seed=9))
+    options = runtime_options(spec.layout(), 5, 30)
+
+    def eager():
+        return backend.execute(backend.prepare(q, k, v, layer_index=0, transformer_options=options))
+
+    first = eager().clone()
+    captured = backend.capture(q, k, v, layer_index=0, transformer_options=options)
+    assert torch.equal(captured.replay(), first)
+    # new contents in the same buffers: the replay recomputes statistics, carriers, route and output
+    q2, k2, v2 = (t.cuda() for t in workloads.gaussian_qkv(spec, seed=10))
+    q.copy_(q2); k.copy_(k2); v.copy_(v2)
+    second = captured.replay().clone()
+    torch.cuda.synchronize()
+    assert not torch.equal(second, first)
+    assert torch.equal(eager(), second)
+    backend.check_status()
