@@ -69,8 +69,6 @@ def parse_args():
     parser.add_argument("--exchange", choices=("auto", "peer", "nccl"), default="auto",
                         help="N > 1: how the head-sharded output is reassembled")
     parser.add_argument("--budget", type=float, default=VIDEO_BUDGET)
-    parser.add_argument("--single-term-p", action="store_true",
-                        help="carry P as one E4M3 term (faster, outside the parity gate on Gaussian V)")
     parser.add_argument("--heads", type=int, default=0,
                         help="run a head subset of the workload (profiling captures); 0 = all heads")
     parser.add_argument("--skip-cpu-baseline", action="store_true")
