@@ -74,10 +74,9 @@ def parse_args():
     parser.add_argument("--skip-cpu-baseline", action="store_true")
     parser.add_argument("--skip-e2e", action="store_true")
     parser.add_argument("--no-graph", action="store_true",
-                        help="time the eager step only; by default a single-GPU run also captures the step into a CUDA "
-                             "graph (backend.capture) and `value` is the replayed step, with the eager figure beside it")
-    parser.add_argument("--graph", action="store_true",
-                        help="multi-GPU runs: capture the step (with its peer-store exchange) too; off by default there")
+                        help="time the eager step only; by default the step (with its peer-store exchange at N > 1) is "
+                             "also captured into a CUDA graph (backend.capture) and `value` is the replayed step, with "
+                             "the eager figure beside it; the NCCL exchange is never captured")
     return parser.parse_args()
 
 
@@ -561,7 +560,7 @@ def run_attention(args, spec, stdout):
     # One layer call is the same ten kernels every sampler step: captured once, a replay costs the host
     # one launch, so a rank whose Python thread is late no longer holds up the barrier of the others.
     launch, graph_ms = "eager: prepare() + execute() per step", None
-    if not args.no_graph and not args.schedule and (world == 1 or (args.graph and args.exchange != "nccl")):
+    if not args.no_graph and not args.schedule and (world == 1 or args.exchange != "nccl"):
         captured, failure = None, None
         try:
             captured = owner.capture(q, k, v, layer_index=0, transformer_options=options[0])
