@@ -129,7 +129,13 @@ def _sharded_worker(rank, world, port, heads, queue):
             sharded.prepare(torch.zeros((1, b - a + 1, sequence, 128)), q, q, layer_index=0, transformer_options={})
         except ValueError:
             wrong = True
-        queue.put((rank, ok and wrong))
+        # the collective path is never recorded into a CUDA graph: capture refuses before it touches anything
+        refused = False
+        try:
+            sharded.capture(q, q, q, layer_index=0, transformer_options={})
+        except RuntimeError as exc:
+            refused = "peer-store exchange" in str(exc)
+        queue.put((rank, ok and wrong and refused))
     finally:
         dist.destroy_process_group()
 
